@@ -85,7 +85,7 @@ class CacheLayout:
                 continue
             if not 0 <= src < n or cache_from[src] is not None or needs[src] is None:
                 raise ValueError(f"layer {i} reads the cache of layer {src}, which owns none")
-            if needs[i] is None or needs[i].group_key()[:3] != needs[src].group_key()[:3]:
+            if needs[i] is None or needs[i].layout_key() != needs[src].layout_key():
                 raise ValueError(f"layer {i} cannot read layer {src}'s cache: their head layouts differ")
             sw, rw = needs[src].window, needs[i].window
             if sw is not None and (rw is None or rw > sw):

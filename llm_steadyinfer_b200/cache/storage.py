@@ -1,6 +1,7 @@
 """Device tensors behind the cache manager: per group one key and one value tensor
-``[layers_in_group, num_pages, kv_heads, page_size, head_dim]`` and, for mixers with
-fixed-size state, one tensor ``[slots, *shape]`` per layer. The reference keeps
+``[layers_in_group, num_pages, kv_heads, page_size, head_dim]`` (values with their own last size, or none at all
+for a group whose keys serve as values) and, for mixers with fixed-size state, one tensor ``[slots, *shape]`` per
+layer; a place of the layout without a mixer (the embedder's, last) has its state here as well. The reference keeps
 ``[L, num_blocks, block_size, kv_dim]`` in fp32 (src/source/scheduler/kv_manager.cpp:41-53);
 here a page holds each head's rows contiguously and has the compute dtype.
 """
@@ -36,16 +37,18 @@ class CacheStorage:
         self.values: List[torch.Tensor] = []
         ps = manager.page_size
         for g, grp in enumerate(manager.groups):
-            shape = (len(grp.layers), grp.pool.num_pages, grp.need.num_kv_heads, ps, grp.need.head_dim)
-            self.keys.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.values.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            shape = (len(grp.layers), grp.pool.num_pages, grp.need.num_kv_heads, ps)
+            self.keys.append(torch.zeros(shape + (grp.need.head_dim,), dtype=dtype, device=self.device))
+            # a group without values of their own (value_dim 0) has no second tensor
+            self.values.append(torch.zeros(shape + (grp.need.v_dim,), dtype=dtype, device=self.device)
+                               if grp.need.v_dim else None)
         self.states: List[Optional[torch.Tensor]] = []
         for s in layout.states:
             self.states.append(None if s is None else torch.zeros(
                 (manager.slots.num_slots, *s.shape), dtype=s.dtype, device=self.device))
 
     def bytes(self) -> int:
-        n = sum(t.numel() * t.element_size() for t in self.keys + self.values)
+        n = sum(t.numel() * t.element_size() for t in self.keys + self.values if t is not None)
         return n + sum(t.numel() * t.element_size() for t in self.states if t is not None)
 
     def zero_new_slots(self) -> None:
@@ -68,6 +71,6 @@ class CacheStorage:
                 views.append(LayerCache(None, None, None, ps, False, self.states[i], None))
                 continue
             j = self.layout.layer_index_in_group[i]
-            views.append(LayerCache(self.keys[g][j], self.values[g][j], tables[g], ps,
+            views.append(LayerCache(self.keys[g][j], None if self.values[g] is None else self.values[g][j], tables[g], ps,
                                     self.layout.cache_from[i] is None, self.states[i], g))
         return views

@@ -52,6 +52,12 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class EmbedderSpec:
+    kind: str = "table"            # registered embedder kind
+    params: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: ``h += mixer(norm(h)); h += ffn(norm(h))`` for arrangement "pre_norm".
 
@@ -61,9 +67,9 @@ class LayerSpec:
     before it in the run order.
     """
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]      # None: the block has the mixer's sublayer only
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     weight_prefix: str
     arrangement: str = "pre_norm"
     cache_from: Optional[int] = None
@@ -86,6 +92,7 @@ class ModelSpec:
     final_norm_name: str = "model.norm."
     lm_head_name: str = "lm_head.weight"
     max_position: int = 0
+    embedder: Optional[EmbedderSpec] = None      # None: the plain table under ``embed_name``
 
 
 class ModelConfig:
@@ -122,8 +129,11 @@ def registered_architectures() -> List[str]:
 
 def config_from_dict(d: Dict[str, Any]) -> ModelConfig:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):       # some designs name themselves with one string
+        archs = [d["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(

@@ -1,0 +1,283 @@
+// Attention over the paged cache in its general form, fp32 arithmetic for fp32 or bf16 storage: the
+// 32-bit path of every attention mixer and the yardstick of the tensor-core kernels of this form
+// (attention_flex.cu). Beyond attention_ref.cu it takes
+//   * a key size dk and a value size dv that differ,
+//   * values that are the first dv entries of the keys (v_cache == nullptr: a latent that serves as both),
+//   * a bias by distance: bias[min(i - j, nd - 1), head] (fp32 table [nd, H]) added to the scaled score,
+//   * a sink per head: exp(sink[h]) joins the softmax denominator once, with no key and no value.
+//     s_j = scale * q_h . K[j, g] + bias[min(pos - j, nd - 1), h],  j in [max(0, pos - window + 1), pos]
+//     out_h = sum_j exp(s_j) V[j, g] / (sum_j exp(s_j) + exp(sink_h))
+// One block per (token row, query head); warp w of 4 walks keys j0 + w, j0 + w + 4, ... with a running
+// maximum, the four partial results are merged at the end, so the order of a row's sums depends on its
+// position alone. The file also holds the two kernels that put a step's keys and values into the pages for
+// mixers that do not rotate them with rope_kv.cu: a plain store with dk != dv, and the latent form (norm of
+// the latent, rotation of the shared key part and of the queries' rotated parts).
+#include "common.cuh"
+#include <math.h>
+
+#define GEN_WARPS 4
+#define GEN_MAX_PER_LANE 20   // key and value sizes up to 640
+
+template <typename T>
+__global__ void __launch_bounds__(GEN_WARPS * 32)
+attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
+                         const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                         const int* __restrict__ block_table, int table_width,
+                         const int* __restrict__ row_seq, const int* __restrict__ positions,
+                         T* __restrict__ out, long long out_row_stride, int num_pages,
+                         int page_size, int num_seqs, int H, int KV, int dk, int dv, float scale,
+                         int window, const float* __restrict__ dist_bias, int nd,
+                         const float* __restrict__ sink, int* status) {
+  extern __shared__ float smem[];   // [GEN_WARPS][dv] accumulators, then m[GEN_WARPS], l[GEN_WARPS]
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = h / (H / KV);
+  const int pos = positions[t];
+  const int seq = row_seq[t];
+  T* o = out + (size_t)t * out_row_stride + (size_t)h * dv;
+  if (seq < 0 || seq >= num_seqs) {      // seq < 0 marks a padding row of a fixed-shape step
+    if (threadIdx.x == 0 && seq >= 0) set_status(status, SI_BAD_SEQ);
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) o[d] = from_f32<T>(0.f);
+    return;
+  }
+  const int* table = block_table + (size_t)seq * table_width;
+  const T* qh = q + (size_t)t * q_row_stride + (size_t)h * dk;
+  const size_t v_stride = v_cache ? dv : dk;
+  const T* vbase = v_cache ? v_cache : k_cache;
+
+  float qr[GEN_MAX_PER_LANE], acc[GEN_MAX_PER_LANE];
+#pragma unroll
+  for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+    const int d = lane + 32 * i;
+    qr[i] = d < dk ? to_f32<T>(qh[d]) : 0.f;
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  const int j0 = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  for (int j = j0 + warp; j <= pos; j += GEN_WARPS) {
+    const int slot = j / page_size;
+    const int page = slot < table_width ? table[slot] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) set_status(status, SI_BAD_PAGE);
+      continue;
+    }
+    const size_t tok = ((size_t)page * KV + g) * page_size + (j - slot * page_size);
+    const T* kp = k_cache + tok * dk;
+    const T* vp = vbase + tok * v_stride;
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dk) dot += qr[i] * to_f32<T>(kp[d]);
+    }
+    dot = warp_sum(dot) * scale;
+    if (dist_bias) dot += dist_bias[(size_t)min(pos - j, nd - 1) * H + h];
+    const float m_new = fmaxf(m, dot);
+    const float corr = expf(m - m_new);
+    const float p = expf(dot - m_new);
+    l = l * corr + p;
+#pragma unroll
+    for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dv) acc[i] = acc[i] * corr + p * to_f32<T>(vp[d]);
+    }
+    m = m_new;
+  }
+  float* sacc = smem;
+  float* sm = smem + GEN_WARPS * dv;
+  float* sl = sm + GEN_WARPS;
+#pragma unroll
+  for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
+    const int d = lane + 32 * i;
+    if (d < dv) sacc[warp * dv + d] = acc[i];
+  }
+  if (lane == 0) { sm[warp] = m; sl[warp] = l; }
+  __syncthreads();
+  float M = sink ? sink[h] : -INFINITY;
+#pragma unroll
+  for (int w = 0; w < GEN_WARPS; ++w) M = fmaxf(M, sm[w]);
+  float L = sink ? expf(sink[h] - M) : 0.f, wgt[GEN_WARPS];
+#pragma unroll
+  for (int w = 0; w < GEN_WARPS; ++w) {
+    wgt[w] = sm[w] == -INFINITY ? 0.f : expf(sm[w] - M);
+    L += sl[w] * wgt[w];
+  }
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < GEN_WARPS; ++w) v += sacc[w * dv + d] * wgt[w];
+    o[d] = from_f32<T>(L > 0.f ? v / L : 0.f);
+  }
+}
+
+SI_EXPORT int si_attention_general(const void* q, int dtype, long long q_row_stride, const void* k_cache,
+                                   const void* v_cache, const int* block_table, int table_width,
+                                   const int* row_seq, const int* positions, void* out,
+                                   long long out_row_stride, int num_pages, int page_size, int num_tokens,
+                                   int num_seqs, int H, int KV, int dk, int dv, float scale, int window,
+                                   const float* dist_bias, int nd, const float* sink, int* status,
+                                   cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (dk > 32 * GEN_MAX_PER_LANE || dv > 32 * GEN_MAX_PER_LANE || dk <= 0 || dv <= 0 || KV <= 0 || H % KV) return -2;
+  if (!v_cache && dv > dk) return -2;
+  if (dist_bias && nd <= 0) return -2;
+  dim3 grid(num_tokens, H);
+  const size_t smem = (size_t)(GEN_WARPS * dv + 2 * GEN_WARPS) * sizeof(float);
+  if (dtype == SI_BF16)
+    attention_general_kernel<__nv_bfloat16><<<grid, GEN_WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+        block_table, table_width, row_seq, positions, (__nv_bfloat16*)out, out_row_stride, num_pages,
+        page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, status);
+  else
+    attention_general_kernel<float><<<grid, GEN_WARPS * 32, smem, stream>>>(
+        (const float*)q, q_row_stride, (const float*)k_cache, (const float*)v_cache, block_table,
+        table_width, row_seq, positions, (float*)out, out_row_stride, num_pages, page_size, num_seqs,
+        H, KV, dk, dv, scale, window, dist_bias, nd, sink, status);
+  return si_last_error();
+}
+
+// ---- stores into the pages -----------------------------------------------------------------------
+
+// The page of (seq, pos), or -1 (with the status word set where that is a fault and not padding).
+__device__ __forceinline__ long long page_of(const int* block_table, int table_width, int num_pages,
+                                             int page_size, int num_seqs, int seq, int pos, int* status) {
+  if (seq < 0) return -1;
+  if (seq >= num_seqs) {
+    if (threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
+    return -1;
+  }
+  const int slot = pos / page_size;
+  const int p = (pos >= 0 && slot < table_width) ? block_table[(size_t)seq * table_width + slot] : -1;
+  if (p < 0 || p >= num_pages) {
+    if (threadIdx.x == 0) set_status(status, SI_BAD_PAGE);
+    return -1;
+  }
+  return p;
+}
+
+// row = [ q: H*dk | k: KV*dk | v: KV*dv ]: k and v of every row go to their page as they are.
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ qkv, long long row_stride, const int* __restrict__ positions,
+                                const int* __restrict__ row_seq, const int* __restrict__ block_table,
+                                int table_width, T* __restrict__ k_cache, T* __restrict__ v_cache, int num_pages,
+                                int page_size, int num_seqs, int H, int KV, int dk, int dv, int* status) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const long long page = page_of(block_table, table_width, num_pages, page_size, num_seqs, row_seq[t], pos, status);
+  if (page < 0) return;
+  const int off = pos % page_size;
+  const T* krow = qkv + (size_t)t * row_stride + (size_t)H * dk;
+  const T* vrow = krow + (size_t)KV * dk;
+  for (int idx = threadIdx.x; idx < KV * dk; idx += blockDim.x) {
+    const int g = idx / dk, c = idx % dk;
+    k_cache[(((size_t)page * KV + g) * page_size + off) * dk + c] = krow[idx];
+  }
+  for (int idx = threadIdx.x; idx < KV * dv; idx += blockDim.x) {
+    const int g = idx / dv, c = idx % dv;
+    v_cache[(((size_t)page * KV + g) * page_size + off) * dv + c] = vrow[idx];
+  }
+}
+
+SI_EXPORT int si_kv_store(const void* qkv, int dtype, long long row_stride, const int* positions, const int* row_seq,
+                          const int* block_table, int table_width, void* k_cache, void* v_cache, int num_pages,
+                          int page_size, int num_tokens, int num_seqs, int H, int KV, int dk, int dv, int* status,
+                          cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (dtype == SI_BF16)
+    si_launch(kv_store_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, stream, (const __nv_bfloat16*)qkv,
+              row_stride, positions, row_seq, block_table, table_width, (__nv_bfloat16*)k_cache,
+              (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, H, KV, dk, dv, status);
+  else
+    si_launch(kv_store_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, (const float*)qkv, row_stride,
+              positions, row_seq, block_table, table_width, (float*)k_cache, (float*)v_cache, num_pages,
+              page_size, num_seqs, H, KV, dk, dv, status);
+  return si_last_error();
+}
+
+// The latent form. Per row:
+//   kv = [ latent: rk | shared key part: dr ]  (row of the down projection)
+//   page[pos] = [ latent / sqrt(mean(latent^2) + eps) * w | rotate(shared part) ]         (one key "head" of rk + dr)
+//   q_full[h] = [ (left as it is: the absorbed plain part, rk) | rotate(q[h, dq:dq + dr]) ]   for every head
+// rotate(): the first rd of the dr entries in rotate-half pairs (i, i + rd/2), angle pos * inv_freq[i] in fp32;
+// the other dr - rd entries pass.
+template <typename T>
+__global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_stride, const T* __restrict__ q,
+                                      long long q_stride, T* __restrict__ q_full, long long qf_stride,
+                                      const float* __restrict__ norm_w, float eps, const float* __restrict__ inv_freq,
+                                      int rd, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                                      const int* __restrict__ block_table, int table_width, T* __restrict__ k_cache,
+                                      int num_pages, int page_size, int num_seqs, int H, int dq, int dr, int rk,
+                                      int* status) {
+  __shared__ float red[33];
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int seq = row_seq[t];
+  const int half = rd / 2;
+  const float fpos = (float)pos;
+  // the queries' rotated parts
+  const T* qrow = q + (size_t)t * q_stride;
+  T* qf = q_full + (size_t)t * qf_stride;
+  for (int idx = threadIdx.x; idx < H * dr; idx += blockDim.x) {
+    const int h = idx / dr, i = idx % dr;
+    const T* src = qrow + (size_t)h * (dq + dr) + dq;
+    float y;
+    if (i < rd) {
+      const int f = i < half ? i : i - half;
+      float s, c;
+      sincosf(fpos * inv_freq[f], &s, &c);
+      const float u = to_f32<T>(src[f]), v = to_f32<T>(src[f + half]);
+      y = i < half ? u * c - v * s : v * c + u * s;
+    } else {
+      y = to_f32<T>(src[i]);
+    }
+    qf[(size_t)h * (rk + dr) + rk + i] = from_f32<T>(y);
+  }
+  if (!k_cache) return;
+  const T* row = kv + (size_t)t * kv_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rk; i += blockDim.x) {
+    const float x = to_f32<T>(row[i]);
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  const long long page = page_of(block_table, table_width, num_pages, page_size, num_seqs, seq, pos, status);
+  if (page < 0) return;
+  T* dst = k_cache + ((size_t)page * page_size + pos % page_size) * (rk + dr);
+  const float rs = 1.f / sqrtf(ss / (float)rk + eps);
+  for (int i = threadIdx.x; i < rk; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(row[i]) * rs * norm_w[i]);
+  for (int i = threadIdx.x; i < dr; i += blockDim.x) {
+    float y;
+    if (i < rd) {
+      const int f = i < half ? i : i - half;
+      float s, c;
+      sincosf(fpos * inv_freq[f], &s, &c);
+      const float u = to_f32<T>(row[rk + f]), v = to_f32<T>(row[rk + f + half]);
+      y = i < half ? u * c - v * s : v * c + u * s;
+    } else {
+      y = to_f32<T>(row[rk + i]);
+    }
+    dst[rk + i] = from_f32<T>(y);
+  }
+}
+
+SI_EXPORT int si_latent_prepare(const void* kv, int dtype, long long kv_stride, const void* q, long long q_stride,
+                                void* q_full, long long qf_stride, const float* norm_w, float eps,
+                                const float* inv_freq, int rd, const int* positions, const int* row_seq,
+                                const int* block_table, int table_width, void* k_cache, int num_pages, int page_size,
+                                int num_tokens, int num_seqs, int H, int dq, int dr, int rk, int* status,
+                                cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (rd < 0 || rd > dr || rd % 2) return -2;
+  if (dtype == SI_BF16)
+    si_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, stream, (const __nv_bfloat16*)kv,
+              kv_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)q_full, qf_stride, norm_w, eps, inv_freq,
+              rd, positions, row_seq, block_table, table_width, (__nv_bfloat16*)k_cache, num_pages, page_size,
+              num_seqs, H, dq, dr, rk, status);
+  else
+    si_launch(latent_prepare_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, (const float*)kv, kv_stride,
+              (const float*)q, q_stride, (float*)q_full, qf_stride, norm_w, eps, inv_freq, rd, positions, row_seq,
+              block_table, table_width, (float*)k_cache, num_pages, page_size, num_seqs, H, dq, dr, rk, status);
+  return si_last_error();
+}

@@ -795,3 +795,188 @@ def attn_portion_tc05(q, k_cache, v_cache, block_table, items, out, page_size: i
              _ptr(block_table), block_table.shape[1], _ptr(items), items.shape[0], _ptr(out), out.stride(0),
              k_cache.shape[0], page_size, num_seqs, H, KV, hs, float(scale), int(window or 0), _ptr(status),
              _stream()), f"attn_portion_tc05(heads={H}, kv_heads={KV}, head_dim={hs}, page_size={page_size})")
+
+
+# ---- general attention, stores, latent form -------------------------------------------------------
+
+def embedding_pair(tokens, positions, row_seq, q_start, slots, last_token, table, pair, out, buckets: int,
+                   mul_prev: int, mul_cur: int, num_seqs: int, status=None) -> None:
+    """out[t,:] (fp32) = table[tokens[t],:] + pair[r_t,:], r_t = (previous token * mul_prev + token * mul_cur) mod
+    buckets, r = buckets for a sequence's first token. ``last_token`` (int32 [slots]) holds every request's latest
+    token between steps; the kernel reads and renews it."""
+    _cuda(tokens, positions, row_seq, q_start, slots, last_token, table, pair, out, status)
+    for t, nm in ((tokens, "tokens"), (positions, "positions"), (row_seq, "row_seq"), (q_start, "q_start"),
+                  (slots, "slots"), (last_token, "last_token")):
+        _i32(t, nm)
+    T, d = out.shape
+    _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous() and pair.is_contiguous()
+          and table.dtype == pair.dtype, "embedding_pair: out must be contiguous fp32, tables contiguous and alike")
+    _need(table.shape[1] == d and pair.shape == (buckets + 1, d) and tokens.numel() == T,
+          "embedding_pair: shape mismatch (the pair table has buckets + 1 rows)")
+    f = _fn("embedding", "si_embedding_pair",
+            [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
+             _c_int, _c_p, _c_p])
+    _check(f(_ptr(tokens), _ptr(positions), _ptr(row_seq), _ptr(q_start), _ptr(slots), _ptr(last_token), _ptr(table),
+             _ptr(pair), _dt(table), _ptr(out), T, d, table.shape[0], int(buckets), int(mul_prev), int(mul_cur),
+             int(num_seqs), _ptr(status), _stream()), "embedding_pair")
+
+
+def _f32v(t, name: str, n=None) -> None:
+    if t is not None:
+        _need(t.dtype == torch.float32 and t.is_contiguous() and (n is None or t.numel() == n),
+              f"{name} must be contiguous fp32" + (f" of {n} elements" if n is not None else ""))
+
+
+def attention_general(q, k_cache, v_cache, block_table, row_seq, positions, out, page_size: int, num_seqs: int,
+                      H: int, KV: int, dk: int, dv: int, scale: float, window: int = 0, dist_bias=None, sink=None,
+                      status=None) -> None:
+    """fp32-arithmetic attention over the paged cache with key size ``dk``, value size ``dv``, values from
+    ``v_cache`` or (None) the first ``dv`` entries of the keys, a bias by distance ``dist_bias`` (fp32 [nd, H],
+    row min(distance, nd - 1)) and a sink per head (fp32 [H]) in the softmax denominator."""
+    _cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, dist_bias, sink, status)
+    _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
+    T = q.shape[0]
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == H * dk and out.shape[1] == H * dv,
+          "attention_general: q must be [T, H*dk], out [T, H*dv]")
+    _need(q.dtype == out.dtype == k_cache.dtype and (v_cache is None or v_cache.dtype == q.dtype),
+          "attention_general: dtypes differ")
+    _need(tuple(k_cache.shape[1:]) == (KV, page_size, dk) and k_cache.is_contiguous(),
+          "attention_general: keys must be [pages, KV, page_size, dk]")
+    if v_cache is not None:
+        _need(tuple(v_cache.shape) == (k_cache.shape[0], KV, page_size, dv) and v_cache.is_contiguous(),
+              "attention_general: values must be [pages, KV, page_size, dv]")
+    nd = 0
+    if dist_bias is not None:
+        _need(dist_bias.dim() == 2 and dist_bias.shape[1] == H, "attention_general: dist_bias must be [nd, H]")
+        _f32v(dist_bias, "dist_bias")
+        nd = dist_bias.shape[0]
+    _f32v(sink, "sink", H)
+    f = _fn("attention_general", "si_attention_general",
+            [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_ptr(q), _dt(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(row_seq), _ptr(positions), _ptr(out), out.stride(0), k_cache.shape[0], page_size, T, num_seqs,
+             H, KV, dk, dv, float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), _ptr(status), _stream()),
+           f"attention_general(dk={dk}, dv={dv})")
+
+
+def kv_store(qkv, positions, row_seq, block_table, k_cache, v_cache, page_size: int, num_seqs: int, H: int,
+             KV: int, dk: int, dv: int, status=None) -> None:
+    """Rows [q: H*dk | k: KV*dk | v: KV*dv]: k and v of every row into its page, unrotated."""
+    _cuda(qkv, positions, row_seq, block_table, k_cache, v_cache, status)
+    _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == H * dk + KV * (dk + dv), "kv_store: row layout")
+    _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and tuple(k_cache.shape[1:]) == (KV, page_size, dk) and tuple(v_cache.shape) == (k_cache.shape[0], KV, page_size, dv),
+          "kv_store: caches must be [pages, KV, page_size, dk] and [pages, KV, page_size, dv]")
+    f = _fn("attention_general", "si_kv_store",
+            [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(positions), _ptr(row_seq), _ptr(block_table), block_table.shape[1],
+             _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], page_size, qkv.shape[0], num_seqs, H, KV, dk, dv,
+             _ptr(status), _stream()), f"kv_store(dk={dk}, dv={dv})")
+
+
+def latent_prepare(kv, q, q_full, norm_w, eps: float, inv_freq, rot_dims: int, positions, row_seq, block_table,
+                   k_cache, page_size: int, num_seqs: int, H: int, dq: int, dr: int, rk: int, status=None) -> None:
+    """The latent attention's step between its projections and the attention itself. ``kv`` [T, rk + dr]: the
+    latent is normalised (weight ``norm_w``) and stored with the rotated shared key part as one key of rk + dr
+    entries (``k_cache`` [pages, 1, page_size, rk + dr]; None: nothing stored). ``q`` [T, H * (dq + dr)]: every head's
+    last dr entries are rotated into ``q_full[:, h, rk:]`` (``q_full`` [T, H * (rk + dr)]; its first rk entries per
+    head are the caller's). The first ``rot_dims`` of the dr entries are rotated in rotate-half pairs."""
+    _cuda(kv, q, q_full, norm_w, inv_freq, positions, row_seq, block_table, k_cache, status)
+    _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
+    T = kv.shape[0]
+    _need(kv.stride(1) == 1 and q.stride(1) == 1 and q_full.stride(1) == 1 and kv.shape[1] == rk + dr
+          and q.shape == (T, H * (dq + dr)) and q_full.shape == (T, H * (rk + dr)), "latent_prepare: shapes")
+    _need(kv.dtype == q.dtype == q_full.dtype, "latent_prepare: dtypes differ")
+    _f32v(norm_w, "norm_w", rk)
+    _f32v(inv_freq, "inv_freq", rot_dims // 2)
+    num_pages = 0
+    if k_cache is not None:
+        _need(k_cache.dtype == kv.dtype and k_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (1, page_size, rk + dr),
+              "latent_prepare: the cache must be [pages, 1, page_size, rk + dr]")
+        num_pages = k_cache.shape[0]
+    f = _fn("attention_general", "si_latent_prepare",
+            [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_f, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p,
+             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(kv), _dt(kv), kv.stride(0), _ptr(q), q.stride(0), _ptr(q_full), q_full.stride(0), _ptr(norm_w),
+             float(eps), _ptr(inv_freq), int(rot_dims), _ptr(positions), _ptr(row_seq), _ptr(block_table),
+             block_table.shape[1] if block_table is not None else 0, _ptr(k_cache), num_pages, page_size, T, num_seqs,
+             H, dq, dr, rk, _ptr(status), _stream()), f"latent_prepare(rank={rk}, rot={dr})")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def activation(x, out, kind: str) -> None:
+    """out = act(x) elementwise on rows (fp32 arithmetic); kinds: relu2 (the square of relu), gelu_tanh, silu, relu."""
+    _cuda(x, out)
+    _need(kind in ACTIVATIONS, f"activation: kind {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    _need(x.dim() == 2 and out.shape == x.shape and x.dtype == out.dtype and x.stride(1) == 1 and out.stride(1) == 1,
+          "activation: x and out must be rows of the same shape and dtype")
+    f = _fn("activation", "si_activation", [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(out), out.stride(0), _dt(x), x.shape[0], x.shape[1], ACTIVATIONS[kind], _stream()),
+           f"activation({kind})")
+
+
+# ---- state-space mixer ---------------------------------------------------------------------------------
+
+def causal_conv(u, weight, bias, state, conv_off: int, out, positions, row_seq, q_start, ctx_len, slots,
+                num_seqs: int, status=None) -> None:
+    """out[t, c] (fp32) = silu(bias[c] + sum_k weight[c, k] * u[t - (K-1) + k, c]) per sequence, zeros before its
+    start; inputs of earlier steps come from ``state[slot, conv_off:]`` ([K-1, C], fp32), which is renewed with
+    this step's last K - 1 inputs afterwards (two launches)."""
+    _cuda(u, weight, bias, state, out, positions, row_seq, q_start, ctx_len, slots, status)
+    for t, nm in ((positions, "positions"), (row_seq, "row_seq"), (q_start, "q_start"), (ctx_len, "ctx_len"), (slots, "slots")):
+        _i32(t, nm)
+    T, C = u.shape
+    K = weight.shape[1]
+    _need(u.stride(1) == 1 and weight.shape == (C, K), "causal_conv: u must be rows [T, C], weight [C, K]")
+    _f32v(weight, "weight"); _f32v(bias, "bias", C)
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, C), "causal_conv: out must be fp32 [T, C]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state.shape[1] >= conv_off + (K - 1) * C, "causal_conv: state must be fp32 [slots, >= conv_off + (K-1)*C]")
+    f = _fn("ssm", "si_causal_conv",
+            [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int,
+             _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(u), _dt(u), u.stride(0), _ptr(weight), _ptr(bias), _ptr(state), state.stride(0), int(conv_off), _ptr(out),
+             _ptr(positions), _ptr(row_seq), _ptr(q_start), _ptr(ctx_len), _ptr(slots), T, int(num_seqs), C, K,
+             _ptr(status), _stream()), f"causal_conv(channels={C}, taps={K})", kernels=2 if K > 1 else 1)
+
+
+def ssm_scan(xbc, dt_raw, dt_bias, a_log, d_skip, state, y, q_start, ctx_len, slots, num_seqs: int, heads: int,
+             groups: int, N: int, P: int) -> None:
+    """The recurrence over every sequence's rows of this step, from and into ``state[slot, :heads*N*P]`` (fp32, from
+    zero for a portion that starts at position 0). ``xbc`` fp32 [T, heads*P + 2*groups*N] = [x | B | C];
+    ``dt_raw`` [T, heads] (compute dtype, a strided view); ``y`` fp32 [T, heads*P]."""
+    _cuda(xbc, dt_raw, dt_bias, a_log, d_skip, state, y, q_start, ctx_len, slots)
+    for t, nm in ((q_start, "q_start"), (ctx_len, "ctx_len"), (slots, "slots")):
+        _i32(t, nm)
+    T = xbc.shape[0]
+    _need(xbc.dtype == torch.float32 and xbc.stride(1) == 1 and xbc.shape[1] == heads * P + 2 * groups * N,
+          "ssm_scan: xbc must be fp32 [T, heads*P + 2*groups*N]")
+    _need(dt_raw.shape == (T, heads) and dt_raw.stride(1) == 1, "ssm_scan: dt_raw must be [T, heads]")
+    _need(y.dtype == torch.float32 and y.shape == (T, heads * P) and y.stride(1) == 1, "ssm_scan: y must be fp32 [T, heads*P]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= heads * N * P,
+          "ssm_scan: state must be fp32 [slots, >= heads*N*P]")
+    _f32v(dt_bias, "dt_bias", heads); _f32v(a_log, "a_log", heads); _f32v(d_skip, "d_skip", heads)
+    f = _fn("ssm", "si_ssm_scan",
+            [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int,
+             _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(xbc), xbc.stride(0), _ptr(dt_raw), _dt(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log),
+             _ptr(d_skip), _ptr(state), state.stride(0), _ptr(y), y.stride(0), _ptr(q_start), _ptr(ctx_len), _ptr(slots),
+             int(num_seqs), heads, groups, N, P, _stream()), f"ssm_scan(heads={heads}, state={N}, head_dim={P})")
+
+
+def gated_part_norm(y, z, weight, out, parts: int, eps: float) -> None:
+    """out = g / sqrt(mean(g^2) + eps) * weight with g = y * silu(z), the mean over each of ``parts`` equal parts of a
+    row. ``y`` fp32 rows, ``z`` and ``out`` rows in the compute dtype (views with a row stride are fine)."""
+    _cuda(y, z, weight, out)
+    T, W = y.shape
+    _need(y.dtype == torch.float32 and y.stride(1) == 1 and z.shape == (T, W) and out.shape == (T, W)
+          and z.stride(1) == 1 and out.stride(1) == 1 and z.dtype == out.dtype, "gated_part_norm: shapes or dtypes")
+    _f32v(weight, "weight", W)
+    f = _fn("ssm", "si_gated_part_norm", [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_ptr(y), y.stride(0), _ptr(z), _dt(z), z.stride(0), _ptr(weight), _ptr(out), out.stride(0), T, W, int(parts),
+             float(eps), _stream()), f"gated_part_norm(width={W}, parts={parts})")

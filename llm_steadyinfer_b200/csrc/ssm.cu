@@ -1,0 +1,292 @@
+// Kernels of the state-space mixer (selective state space with a scalar decay per head) and of the short causal
+// convolution in front of it. Everything that enters the recurrence is fp32: the step size, the decay, the state
+// and the sums; the inputs are the projection's output in the compute dtype.
+//
+// Per request the mixer keeps one fp32 vector in its state slot:
+//   [ recurrent state: heads * N * P | the convolution's last K - 1 inputs: (K - 1) * C ]
+// A portion of a sequence starts from what the slot holds (from zero when the portion starts at position 0) and
+// leaves behind what the next portion needs, so a sequence may be cut anywhere.
+//
+//   conv:  y[t, c] = act(b[c] + sum_k w[c, k] * u[t - (K - 1) + k, c]),   u = 0 before the sequence
+//   scan:  S_t = exp(-exp(a_log_h) * dt_t) * S_{t-1} + dt_t * B_t x_t^T   (S is N x P, per head h)
+//          y_t = S_t^T C_t + D_h x_t,   dt_t = softplus(raw_t + dt_bias_h),   B, C of group h / (heads / groups)
+//   gate:  g = y * silu(z);  out = g / sqrt(mean_part(g^2) + eps) * w     over `parts` equal parts of a row
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---- causal convolution + silu -------------------------------------------------------------------------------
+// One thread per (row, channel). Inputs of earlier steps come from the slot's conv part [K - 1, C] (oldest
+// first), those of this step from the rows before this one in the same portion.
+template <typename T>
+__global__ void causal_conv_kernel(const T* __restrict__ u, long long u_stride, const float* __restrict__ w,
+                                   const float* __restrict__ b, const float* __restrict__ state,
+                                   long long state_stride, long long conv_off, float* __restrict__ out,
+                                   const int* __restrict__ positions, const int* __restrict__ row_seq,
+                                   const int* __restrict__ q_start, const int* __restrict__ slots, int num_seqs,
+                                   int C, int K, int* status) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seq = row_seq[t];
+  if (seq < 0 || seq >= num_seqs) {
+    if (seq >= 0 && threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
+    out[(size_t)t * C + c] = 0.f;
+    return;
+  }
+  const int pos = positions[t];
+  const int back = t - q_start[seq];                  // rows of this portion before this one
+  const float* st = state + (size_t)slots[seq] * state_stride + conv_off;
+  float acc = b[c];
+  for (int k = 0; k < K; ++k) {
+    const int j = K - 1 - k;                          // the input j tokens back
+    float x;
+    if (j > pos) x = 0.f;
+    else if (j <= back) x = to_f32<T>(u[(size_t)(t - j) * u_stride + c]);
+    else x = st[(size_t)(K - 1 - (j - back)) * C + c];    // j - back tokens before the portion
+    acc = fmaf(w[(size_t)c * K + k], x, acc);
+  }
+  out[(size_t)t * C + c] = silu_f(acc);
+}
+
+// After the convolution of a step: the slot keeps the last K - 1 inputs of every sequence of the step.
+// One thread per (sequence, channel); it reads what it needs of the old contents before it writes.
+#define CONV_MAX_TAPS 16
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ u, long long u_stride, float* __restrict__ state,
+                                  long long state_stride, long long conv_off, const int* __restrict__ q_start,
+                                  const int* __restrict__ ctx_len, const int* __restrict__ slots, int C, int K) {
+  pdl_prologue();
+  const int s = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int row0 = q_start[s], n = q_start[s + 1] - row0;
+  if (n <= 0) return;
+  const int pos0 = ctx_len[s] - n;
+  float* st = state + (size_t)slots[s] * state_stride + conv_off;
+  float keep[CONV_MAX_TAPS];
+  const int H = K - 1;
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+    if (i >= H) break;
+    // new entry i is the input at position pos0 + n - H + i
+    const int r = n - H + i;                          // row within the portion, negative: before it
+    float x;
+    if (r >= 0) x = to_f32<T>(u[(size_t)(row0 + r) * u_stride + c]);
+    else if (pos0 + r < 0) x = 0.f;
+    else x = st[(size_t)(H + r) * C + c];
+    keep[i] = x;
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+    if (i >= H) break;
+    st[(size_t)i * C + c] = keep[i];
+  }
+}
+
+SI_EXPORT int si_causal_conv(const void* u, int dtype, long long u_stride, const float* w, const float* b,
+                             float* state, long long state_stride, long long conv_off, float* out,
+                             const int* positions, const int* row_seq, const int* q_start, const int* ctx_len,
+                             const int* slots, int num_tokens, int num_seqs, int C, int K, int* status,
+                             cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (K < 1 || K - 1 > CONV_MAX_TAPS || C > 65535 * 128 || num_seqs > 65535) return -2;
+  const int threads = 128;
+  dim3 grid(num_tokens, (C + threads - 1) / threads);
+  dim3 sgrid((C + threads - 1) / threads, num_seqs);
+  if (dtype == SI_BF16) {
+    si_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)u, u_stride, w, b,
+              (const float*)state, state_stride, conv_off, out, positions, row_seq, q_start, slots, num_seqs, C, K, status);
+    if (K > 1)
+      si_launch(conv_state_kernel<__nv_bfloat16>, sgrid, dim3(threads), 0, stream, (const __nv_bfloat16*)u, u_stride, state,
+                state_stride, conv_off, q_start, ctx_len, slots, C, K);
+  } else {
+    si_launch(causal_conv_kernel<float>, grid, dim3(threads), 0, stream, (const float*)u, u_stride, w, b,
+              (const float*)state, state_stride, conv_off, out, positions, row_seq, q_start, slots, num_seqs, C, K, status);
+    if (K > 1)
+      si_launch(conv_state_kernel<float>, sgrid, dim3(threads), 0, stream, (const float*)u, u_stride, state,
+                state_stride, conv_off, q_start, ctx_len, slots, C, K);
+  }
+  return si_last_error();
+}
+
+// ---- the recurrence -------------------------------------------------------------------------------------------
+// One block per (sequence of the step, head). Thread (p, ns) keeps NPT entries S[ns * NPT + i, p] of the state in
+// registers; the NS threads of one p are neighbouring lanes and add their parts of y_t with shuffles. Tokens are
+// walked in order, SCAN_CHUNK at a time staged in shared memory (B, C, x, step size, decay).
+#define SCAN_CHUNK 16
+
+template <typename T, int NPT>
+__global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_stride,     // conv output: [x | B | C]
+                                const T* __restrict__ dt_raw, long long dt_stride,
+                                const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                const float* __restrict__ Dskip, float* __restrict__ state, long long state_stride,
+                                float* __restrict__ y, long long y_stride, const int* __restrict__ q_start,
+                                const int* __restrict__ ctx_len, const int* __restrict__ slots, int heads,
+                                int groups, int N, int P, int NS) {
+  extern __shared__ float sm[];
+  pdl_prologue();
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int row0 = q_start[s], n_rows = q_start[s + 1] - row0;
+  if (n_rows <= 0) return;
+  const int pos0 = ctx_len[s] - n_rows;
+  const int g = h / (heads / groups);
+  const int inner = heads * P;
+  float* sB = sm;                              // [SCAN_CHUNK][Npad]
+  const int Npad = NS * NPT;
+  float* sC = sB + SCAN_CHUNK * Npad;
+  float* sX = sC + SCAN_CHUNK * Npad;          // [SCAN_CHUNK][P], already times the step size
+  float* sXr = sX + SCAN_CHUNK * P;            // [SCAN_CHUNK][P], as it came (for the skip term)
+  float* sDec = sXr + SCAN_CHUNK * P;          // [SCAN_CHUNK]
+  const int tid = threadIdx.x;
+  const int ns = tid % NS;
+  const bool live = tid / NS < P;          // the last warp may hold threads beyond the state's columns: they follow idly
+  const int p = live ? tid / NS : 0;
+  float* st = state + (size_t)slots[s] * state_stride + (size_t)h * N * P;
+  float S[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = ns * NPT + i;
+    S[i] = (live && n < N && pos0 > 0) ? st[(size_t)n * P + p] : 0.f;
+  }
+  const float rate = expf(a_log[h]);
+  const float bias = dt_bias[h];
+  const float dskip = Dskip[h];
+  for (int c0 = 0; c0 < n_rows; c0 += SCAN_CHUNK) {
+    const int cn = min(SCAN_CHUNK, n_rows - c0);
+    __syncthreads();
+    for (int idx = tid; idx < cn; idx += blockDim.x) {
+      const float dt = softplus_f(to_f32<T>(dt_raw[(size_t)(row0 + c0 + idx) * dt_stride + h]) + bias);
+      sDec[idx] = expf(-rate * dt);
+      sDec[SCAN_CHUNK + idx] = dt;
+    }
+    for (int idx = tid; idx < cn * Npad; idx += blockDim.x) {
+      const int r = idx / Npad, n = idx % Npad;
+      const float* src = xbc + (size_t)(row0 + c0 + r) * xbc_stride + inner + (size_t)g * N;
+      sB[idx] = n < N ? src[n] : 0.f;
+      sC[idx] = n < N ? src[(size_t)groups * N + n] : 0.f;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < cn * P; idx += blockDim.x) {
+      const int r = idx / P, pp = idx % P;
+      const float x = xbc[(size_t)(row0 + c0 + r) * xbc_stride + (size_t)h * P + pp];
+      sXr[idx] = x;
+      sX[idx] = x * sDec[SCAN_CHUNK + r];
+    }
+    __syncthreads();
+    {
+      for (int r = 0; r < cn; ++r) {
+        const float dec = sDec[r];
+        const float dx = sX[r * P + p];
+        const float* Br = sB + r * Npad + ns * NPT;
+        const float* Cr = sC + r * Npad + ns * NPT;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+          S[i] = fmaf(dec, S[i], dx * Br[i]);
+          acc = fmaf(S[i], Cr[i], acc);
+        }
+        for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, NS);
+        if (ns == 0 && live) y[(size_t)(row0 + c0 + r) * y_stride + (size_t)h * P + p] = acc + dskip * sXr[r * P + p];
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = ns * NPT + i;
+      if (n < N) st[(size_t)n * P + p] = S[i];
+    }
+  }
+}
+
+template <typename T, int NPT>
+static int scan_launch(const float* xbc, long long xbc_stride, const void* dt_raw, long long dt_stride,
+                       const float* dt_bias, const float* a_log, const float* Dskip, float* state,
+                       long long state_stride, float* y, long long y_stride, const int* q_start, const int* ctx_len,
+                       const int* slots, int num_seqs, int heads, int groups, int N, int P, int NS, cudaStream_t stream) {
+  int threads = (P * NS + 31) / 32 * 32;
+  const size_t smem = (size_t)(2 * SCAN_CHUNK * NS * NPT + 2 * SCAN_CHUNK * P + 2 * SCAN_CHUNK) * sizeof(float);
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(ssm_scan_kernel<T, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return -2;
+  }
+  si_launch(ssm_scan_kernel<T, NPT>, dim3(num_seqs, heads), dim3(threads), smem, stream, xbc, xbc_stride,
+            (const T*)dt_raw, dt_stride, dt_bias, a_log, Dskip, state, state_stride, y, y_stride, q_start, ctx_len,
+            slots, heads, groups, N, P, NS);
+  return si_last_error();
+}
+
+SI_EXPORT int si_ssm_scan(const float* xbc, long long xbc_stride, const void* dt_raw, int dtype, long long dt_stride,
+                          const float* dt_bias, const float* a_log, const float* Dskip, float* state,
+                          long long state_stride, float* y, long long y_stride, const int* q_start,
+                          const int* ctx_len, const int* slots, int num_seqs, int heads, int groups, int N, int P,
+                          cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || P > 1024 || heads > 65535) return -2;
+  // lanes per column of the state: a power of two up to 32, as many as keep the block within 1024 threads and give
+  // every thread at most 32 state entries
+  int NS = 32;
+  while (NS > 1 && (P * NS > 1024 || NS * 2 > N)) NS >>= 1;
+  while (NS > 1 && P * NS > 512 && (N + NS / 2 - 1) / (NS / 2) <= 16) NS >>= 1;     // fewer, fuller threads
+  const int per = (N + NS - 1) / NS;
+  if (per > 32) return -2;
+#define SCAN_GO(TT, NPT) scan_launch<TT, NPT>(xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, Dskip, state, \
+                                              state_stride, y, y_stride, q_start, ctx_len, slots, num_seqs, heads, \
+                                              groups, N, P, NS, stream)
+  if (dtype == SI_BF16) {
+    if (per <= 4) return SCAN_GO(__nv_bfloat16, 4);
+    if (per <= 8) return SCAN_GO(__nv_bfloat16, 8);
+    if (per <= 16) return SCAN_GO(__nv_bfloat16, 16);
+    return SCAN_GO(__nv_bfloat16, 32);
+  }
+  if (per <= 4) return SCAN_GO(float, 4);
+  if (per <= 8) return SCAN_GO(float, 8);
+  if (per <= 16) return SCAN_GO(float, 16);
+  return SCAN_GO(float, 32);
+#undef SCAN_GO
+}
+
+// ---- gate and norm in parts -----------------------------------------------------------------------------------
+// One block per (row, part): g = y * silu(z); out = g / sqrt(mean(g^2) + eps) * w.
+template <typename T>
+__global__ void gated_part_norm_kernel(const float* __restrict__ y, long long y_stride, const T* __restrict__ z,
+                                       long long z_stride, const float* __restrict__ w, T* __restrict__ out,
+                                       long long out_stride, int part, float eps) {
+  __shared__ float red[33];
+  pdl_prologue();
+  const int t = blockIdx.x, c0 = blockIdx.y * part;
+  const float* yr = y + (size_t)t * y_stride + c0;
+  const T* zr = z + (size_t)t * z_stride + c0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < part; i += blockDim.x) {
+    const float g = yr[i] * silu_f(to_f32<T>(zr[i]));
+    ss += g * g;
+  }
+  ss = block_sum(ss, red);
+  const float rs = 1.f / sqrtf(ss / (float)part + eps);
+  T* o = out + (size_t)t * out_stride + c0;
+  for (int i = threadIdx.x; i < part; i += blockDim.x) {
+    const float g = yr[i] * silu_f(to_f32<T>(zr[i]));
+    o[i] = from_f32<T>(g * rs * w[c0 + i]);
+  }
+}
+
+SI_EXPORT int si_gated_part_norm(const float* y, long long y_stride, const void* z, int dtype, long long z_stride,
+                                 const float* w, void* out, long long out_stride, int rows, int width, int parts,
+                                 float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (parts <= 0 || width % parts || parts > 65535) return -2;
+  const int part = width / parts;
+  const int threads = part >= 512 ? 256 : 128;
+  if (dtype == SI_BF16)
+    si_launch(gated_part_norm_kernel<__nv_bfloat16>, dim3(rows, parts), dim3(threads), 0, stream, y, y_stride,
+              (const __nv_bfloat16*)z, z_stride, w, (__nv_bfloat16*)out, out_stride, part, eps);
+  else
+    si_launch(gated_part_norm_kernel<float>, dim3(rows, parts), dim3(threads), 0, stream, y, y_stride,
+              (const float*)z, z_stride, w, (float*)out, out_stride, part, eps);
+  return si_last_error();
+}

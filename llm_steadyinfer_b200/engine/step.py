@@ -131,8 +131,8 @@ class ModelRunner:
             if not earlier:
                 raise StepError(f"layer {i} reads the cache of layer {src}, which does not run before it")
             cache_from.append(earlier[-1])
-        self.layout = CacheLayout([model.blocks[i].mixer.cache_need() for i in order],
-                                  [model.blocks[i].mixer.state_need() for i in order], cache_from)
+        needs, states = model.cache_places()          # the run order's places, then the embedder's
+        self.layout = CacheLayout(needs, states, cache_from + [None] * (len(needs) - len(cache_from)))
         self.manager = CacheManager(self.layout, page_size, num_pages, max_requests, prefix_reuse)
         self.storage = CacheStorage(self.layout, self.manager, model.dtype, self.device)
         self.page_size = page_size

@@ -1,2 +1,2 @@
-from . import llama  # noqa: F401  (registers "LlamaForCausalLM")
+from . import llama, mivorax  # noqa: F401  (register "LlamaForCausalLM", "Mivorax")
 from .model import Model

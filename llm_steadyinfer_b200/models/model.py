@@ -12,9 +12,9 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..config.base import ModelConfig, ModelSpec
+from ..config.base import EmbedderSpec, ModelConfig, ModelSpec
 from ..csrc import ops
-from ..parts import Block, feed_forward_class, mixer_class, norm_class, position_class
+from ..parts import Block, embedder_class, feed_forward_class, mixer_class, norm_class, position_class
 from ..parts.linear import configure_library_gemm, linear
 from ..engine import tracing
 
@@ -34,13 +34,23 @@ class Model:
             if ls.mixer.position is not None:
                 pos = position_class(ls.mixer.position.kind)(ls.mixer.position.params, dtype, self.device)
             mixer = mixer_class(ls.mixer.kind)(ls.mixer.params, dtype, self.device, position=pos)
-            ffn = feed_forward_class(ls.feed_forward.kind)(ls.feed_forward.params, dtype, self.device)
+            ffn = n2 = None
+            if ls.feed_forward is not None:
+                ffn = feed_forward_class(ls.feed_forward.kind)(ls.feed_forward.params, dtype, self.device)
+                n2 = norm_class(ls.feed_forward_norm.kind)(ls.feed_forward_norm.params, dtype, self.device)
             n1 = norm_class(ls.mixer_norm.kind)(ls.mixer_norm.params, dtype, self.device)
-            n2 = norm_class(ls.feed_forward_norm.kind)(ls.feed_forward_norm.params, dtype, self.device)
             self.blocks.append(Block(mixer, ffn, n1, n2, ls.arrangement))
         self.final_norm = norm_class(self.spec.final_norm.kind)(self.spec.final_norm.params, dtype, self.device)
+        # the embedder: by default the plain table under the spec's embedding name
+        es = self.spec.embedder or EmbedderSpec("table", {})
+        self._embed_prefix, _, last = self.spec.embed_name.rpartition(".")
+        self._embed_prefix += "." if self._embed_prefix else ""
+        eparams = {"vocab_size": self.spec.vocab_size, "hidden_size": self.spec.hidden_size, "name": last}
+        eparams.update(es.params)
+        self.embedder = embedder_class(es.kind)(eparams, dtype, self.device)
         self.embed: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
+        self._layer_hook = None
         for i in self.spec.order:
             if not 0 <= i < len(self.blocks):
                 raise ValueError(f"run order names layer {i}, but the model has {len(self.blocks)} layers")
@@ -50,14 +60,16 @@ class Model:
         for ls, b in zip(self.spec.layers, self.blocks):
             p = ls.weight_prefix
             yield p + ls.mixer_prefix, b.mixer
-            yield p + ls.feed_forward_prefix, b.feed_forward
             yield p + ls.mixer_norm_name, b.mixer_norm
-            yield p + ls.feed_forward_norm_name, b.feed_forward_norm
+            if b.feed_forward is not None:
+                yield p + ls.feed_forward_prefix, b.feed_forward
+                yield p + ls.feed_forward_norm_name, b.feed_forward_norm
         yield self.spec.final_norm_name, self.final_norm
+        yield self._embed_prefix, self.embedder
 
     def weight_shapes(self) -> Dict[str, Tuple[int, ...]]:
         """Every checkpoint tensor the model wants: full name -> shape."""
-        shapes = {self.spec.embed_name: (self.spec.vocab_size, self.spec.hidden_size)}
+        shapes = {}
         if not self.spec.tie_word_embeddings:
             shapes[self.spec.lm_head_name] = (self.spec.vocab_size, self.spec.hidden_size)
         for prefix, part in self._named_parts():
@@ -75,17 +87,25 @@ class Model:
                 return part.keeps_dtype(name[len(prefix):])
         return False
 
+    def norm_like(self, name: str) -> bool:
+        """True for tensors that random weights draw around one (norm weights), as far as the owning part says
+        (``Part.norm_like``; by default the vectors that keep their dtype)."""
+        for prefix, part in self._named_parts():
+            if name.startswith(prefix) and name[len(prefix):] in part.weight_shapes():
+                return part.norm_like(name[len(prefix):])
+        return False
+
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         """``tensors`` holds every name of ``weight_shapes`` on the device, matrices in the
         compute dtype."""
-        self.embed = tensors[self.spec.embed_name].contiguous()
-        self.lm_head = self.embed if self.spec.tie_word_embeddings else tensors[self.spec.lm_head_name].contiguous()
         for prefix, part in self._named_parts():
             part.load_weights({n: tensors[prefix + n] for n in part.weight_shapes()})
+        self.embed = self.embedder.table
+        self.lm_head = self.embed if self.spec.tie_word_embeddings else tensors[self.spec.lm_head_name].contiguous()
 
     def kernel_files(self, page_size: int) -> List[str]:
         """CUDA sources of the model's own kernels and of its parts (see ``Part.kernel_files``)."""
-        names = {"embedding", "sampling"} | ({"gemm_f32"} if self.dtype == torch.float32 else {"gemm_skinny", "gemm_rows", "gemm_tc05"})
+        names = {"sampling"} | ({"gemm_f32"} if self.dtype == torch.float32 else {"gemm_skinny", "gemm_rows", "gemm_tc05"})
         for _, part in self._named_parts():
             names.update(part.kernel_files(page_size))
         return sorted(names)
@@ -93,6 +113,19 @@ class Model:
     def capturable(self) -> bool:
         """True if every part's ``forward`` may be captured into a CUDA graph (see ``Part.capturable``)."""
         return all(part.capturable for _, part in self._named_parts()) and all(b.capturable for b in self.blocks)
+
+    def hook_layers(self, fn) -> None:
+        """``fn(run, resid)`` is called after every layer run with the fp32 residual stream as it then stands, the
+        run's own pending delta added (tests compare layer by layer through this); None takes the hook off."""
+        self._layer_hook = fn
+
+    # ---- cache and state --------------------------------------------------------------
+    def cache_places(self):
+        """What the cache layout is made of: (cache needs, state needs) per place. The places are the run order's,
+        then one for the embedder (it keeps no pages, but may keep state per request)."""
+        mixers = [self.blocks[i].mixer for i in self.spec.order]
+        return ([m.cache_need() for m in mixers] + [None],
+                [m.state_need() for m in mixers] + [self.embedder.state_need()])
 
     # ---- forward -------------------------------------------------------------------
     def prepare(self, ctx, caches) -> None:
@@ -107,7 +140,7 @@ class Model:
         place in the run order (a layer that runs twice has a cache per run)."""
         T, d = ctx.num_tokens, self.spec.hidden_size
         resid = ctx.buf("resid", (T, d), torch.float32)
-        ops.embedding_gather(ctx.tokens, self.embed, resid, status=ctx.status)
+        self.embedder.forward(ctx, resid, caches[len(self.spec.order)].state)
         delta = None
         for o, i in enumerate(self.spec.order):
             if tracing.ENABLED:
@@ -115,6 +148,8 @@ class Model:
                     delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
             else:
                 delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
+            if self._layer_hook is not None:
+                self._layer_hook(o, resid if delta is None else resid + delta.float())
         R = ctx.num_logit_rows
         if R == 0:
             return None

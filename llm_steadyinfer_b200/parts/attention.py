@@ -1,12 +1,27 @@
-"""Attention mixer: grouped-query causal attention over the paged cache, optional window.
+"""Attention mixer: grouped-query causal attention over the paged cache, optional window, optional learned bias by
+distance, a value size that may differ from the key size.
 
 Per row: q, k, v from one stacked projection [ (H + 2 KV) * hs, d ] (the reference stacks
 them too, src/source/model/llama3.cpp:434-498, but then reads the output with the wrong row
 stride, llama3.cpp:1009-1019; every consumer here takes the row stride); rotation of q and k
 and the store of k, v into the sequence's pages; softmax(scale * q . K) V over cache
 positions up to the row's own (llama3.cpp:1048-1067); output projection (llama3.cpp:1136-1140).
+
+Options beyond the reference's block, all parameters of the part:
+``value_dim``      size of a value head (default ``head_dim``); the cache then keeps values of that size.
+``distance_bias``  ``{"max_distance": D, "buckets": B or None, "name": tensor}``: a learned table [B, heads] whose row
+                   ``bucket(i - j)`` is added to the scaled score of query i and key j. Distances below B/2 have a
+                   row each; the other B - B/2 rows share the distances from B/2 to D on a logarithmic scale:
+                   ``bucket(n) = min(B - 1, B/2 + floor(log(n / (B/2)) / log(D / (B/2)) * (B - B/2)))``. B None: the
+                   checkpoint's tensor says how many rows there are. At load the table is spread out by distance
+                   (one row for every n up to D), which is what the kernels index.
+``names``          checkpoint names of the four matrices, ``{"q": .., "k": .., "v": .., "o": ..}``.
+With either of the first two the mixer runs the general attention kernels (``attention_general.cu`` in 32-bit,
+``attention_flex.cu`` on the tensor cores in bfloat16) instead of the rotary ones.
 """
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -41,22 +56,46 @@ class Attention(Mixer):
             raise ValueError(f"attention: {self.H} heads are not a multiple of {self.KV} kv heads")
         if self.hs > 256:
             raise ValueError(f"attention: head_dim {self.hs} above 256 is not supported")
+        self.vs = int(params.get("value_dim") or self.hs)
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight"}
+        self.names.update(params.get("names") or {})
+        self.bias_spec = params.get("distance_bias") or None
+        if self.bias_spec is not None:
+            self.bias_name = self.bias_spec.get("name", "distance_bias")
+            self.bias_rows = self.bias_spec.get("buckets")
+            self.bias_max = float(self.bias_spec["max_distance"])
+        self.general = self.bias_spec is not None or self.vs != self.hs
+        if self.general and position is not None:
+            raise ValueError("attention: a distance bias or a value size of its own goes without a position encoding")
+        self.dist_bias = None            # fp32 [distances, H], made at load
         self.qkv = None
         self.o = None
 
     def weight_shapes(self):
-        return {"q_proj.weight": (self.H * self.hs, self.hidden),
-                "k_proj.weight": (self.KV * self.hs, self.hidden),
-                "v_proj.weight": (self.KV * self.hs, self.hidden),
-                "o_proj.weight": (self.hidden, self.H * self.hs)}
+        n = self.names
+        shapes = {n["q"]: (self.H * self.hs, self.hidden),
+                  n["k"]: (self.KV * self.hs, self.hidden),
+                  n["v"]: (self.KV * self.vs, self.hidden),
+                  n["o"]: (self.hidden, self.H * self.vs)}
+        if self.bias_spec is not None:
+            shapes[self.bias_name] = (self.bias_rows if self.bias_rows else -1, self.H)   # -1: as the checkpoint has it
+        return shapes
+
+    def keeps_dtype(self, name):
+        return self.bias_spec is not None and name == self.bias_name
+
+    def norm_like(self, name):
+        return False
 
     def load_weights(self, tensors):
-        self.qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
-                              tensors["v_proj.weight"]], 0).contiguous()
-        self.o = tensors["o_proj.weight"].contiguous()
+        n = self.names
+        self.qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], 0).contiguous()
+        self.o = tensors[n["o"]].contiguous()
+        if self.bias_spec is not None:
+            self.dist_bias = spread_by_distance(tensors[self.bias_name].float(), self.bias_max)
 
     def cache_need(self):
-        return CacheNeed(self.KV, self.hs, self.window)
+        return CacheNeed(self.KV, self.hs, self.window, None if self.vs == self.hs else self.vs)
 
     @property
     def capturable(self):
@@ -69,6 +108,8 @@ class Attention(Mixer):
         return self.qkv if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
 
     def kernel_files(self, page_size):
+        if self.general:
+            return ("attention_general",) + (("gemm_f32",) if self.dtype == torch.float32 else ("gemm_skinny", "gemm_rows", "gemm_tc05"))
         names = ["rope_kv"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_skinny", "gemm_rows", "gemm_tc05"])
         if not self.uses_tensor_cores():
             return tuple(names + ["attention_ref"])
@@ -78,6 +119,8 @@ class Attention(Mixer):
         return tuple(names)
 
     def forward(self, x, ctx, cache, resid=None):
+        if self.general:
+            return self.forward_general(x, ctx, cache)
         T = x.shape[0]
         H, KV, hs = self.H, self.KV, self.hs
         qkv = ctx.buf("attn_qkv", (T, (H + 2 * KV) * hs), self.dtype)
@@ -110,19 +153,36 @@ class Attention(Mixer):
         linear(attn, self.o, out, ctx.status)
         return out
 
+    def forward_general(self, x, ctx, cache):
+        """No rotation; keys and values of their own sizes into the pages as they are; scores with the bias."""
+        T = x.shape[0]
+        H, KV, hs, vs = self.H, self.KV, self.hs, self.vs
+        qkv = ctx.buf("attn_qkv", (T, H * hs + KV * (hs + vs)), self.dtype)
+        linear(x, self.qkv, qkv, ctx.status)
+        if cache.writes:
+            ops.kv_store(qkv, ctx.positions, ctx.row_seq, cache.block_table, cache.k, cache.v, cache.page_size,
+                         ctx.seq_slots, H, KV, hs, vs, status=ctx.status)
+        attn = ctx.buf("attn_out", (T, H * vs), self.dtype)
+        ops.attention_general(qkv[:, :H * hs], cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions, attn,
+                              cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale, self.window or 0,
+                              dist_bias=self.dist_bias, status=ctx.status)
+        out = ctx.buf("delta", (T, self.hidden), self.dtype)
+        linear(attn, self.o, out, ctx.status)
+        return out
+
     # ---- kernels ---------------------------------------------------------------------
     def target_blocks(self) -> int:
         """Decode attention blocks that run at once on this part's device."""
         return DECODE_BLOCKS_PER_SM * ops.sm_count(self.device)
 
     def uses_tensor_cores(self) -> bool:
-        return self.dtype == torch.bfloat16 and USE_TENSOR_CORES and self.hs % 16 == 0
+        return not self.general and self.dtype == torch.bfloat16 and USE_TENSOR_CORES and self.hs % 16 == 0
 
     def prepare(self, ctx, cache):
         """Cut the step's sequences into work items for the tensor-core kernels: runs of few
         tokens (decode rows) for the decode kernel, longer portions in runs of the portion
         kernel's item size. One plan serves every layer with the same head layout and window."""
-        if not self.uses_tensor_cores():
+        if self.general or not self.uses_tensor_cores():
             return
         key = ("attention", self.H, self.KV, self.hs, self.window)
         if key in ctx.plans or cache.k is None:
@@ -208,6 +268,26 @@ class Attention(Mixer):
         if plan["por"] is not None:
             portion = ops.attn_portion_tc05 if plan["tc05"] else ops.attn_portion
             portion(q, cache.k, cache.v, cache.block_table, plan["por"], out, *args, status=ctx.status)
+
+
+def distance_bucket(n: int, rows: int, max_distance: float) -> int:
+    """Row of a bias table of ``rows`` rows for distance n: its own row below rows/2, then logarithmic steps that
+    reach the last row at ``max_distance``."""
+    half = rows // 2
+    if n < half:
+        return n
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(max_distance / half) * (rows - half))))
+
+
+def spread_by_distance(table: torch.Tensor, max_distance: float) -> torch.Tensor:
+    """fp32 [nd, H] with row n = table[bucket(n)] for every distance up to ``max_distance`` rounded up; distances
+    beyond that share the last row, which is what the kernels' ``min(distance, nd - 1)`` gives them."""
+    rows = table.shape[0]
+    if rows < 2 or max_distance <= rows // 2:
+        raise ValueError(f"attention: a bias table of {rows} rows needs max_distance above {rows // 2}, found {max_distance}")
+    nd = int(math.ceil(max_distance)) + 1
+    idx = torch.tensor([distance_bucket(n, rows, max_distance) for n in range(nd)], dtype=torch.long, device=table.device)
+    return table.float().index_select(0, idx).contiguous()
 
 
 register_mixer("attention", Attention)

@@ -8,6 +8,8 @@ know which model or layer it sits in. Four kinds exist:
 ``PositionEncoding``  gives a mixer what it needs to encode positions: ``rotary()`` returns
                       ``(inv_freq, rot_dim)`` for mixers that fuse the rotation, or None, in
                       which case the mixer calls ``apply(q, k, ctx)`` on unfused views.
+``Embedder``          ``forward(ctx, out, state)``: the step's token rows into the fp32 residual stream; it may keep
+                      per-request state of fixed size too (``state_need()``).
 ``Mixer``             ``forward(x, ctx, cache) -> delta`` mixes token rows of a sequence. A mixer or
                       feed-forward that says ``adds_into_residual = True`` is also given ``resid=`` (the fp32
                       stream) and may add its result there itself and return None (its last product then does
@@ -36,15 +38,25 @@ import torch
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Paged keys and values of one layer: pages of [num_kv_heads, page_size, head_dim],
-    one for keys and one for values. ``window`` None keeps every token; otherwise pages
-    that lie wholly before ``position - window + 1`` are given back."""
+    """Paged keys and values of one layer: pages of [num_kv_heads, page_size, head_dim] for keys and
+    [num_kv_heads, page_size, value_dim] for values. ``window`` None keeps every token; otherwise pages
+    that lie wholly before ``position - window + 1`` are given back. ``value_dim`` None: as ``head_dim``;
+    0: the layer keeps no values of their own (a latent that serves as key and value)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else int(self.value_dim)
+
+    def layout_key(self) -> Tuple:
+        """What two layers must share for one to read the other's pages."""
+        return ("paged_kv", self.num_kv_heads, self.head_dim, self.v_dim)
 
     def group_key(self) -> Tuple:
-        return ("paged_kv", self.num_kv_heads, self.head_dim, self.window)
+        return self.layout_key() + (self.window,)
 
 
 @dataclass(frozen=True)
@@ -81,6 +93,10 @@ class Part:
         """True for tensors that stay in the dtype they are stored in (vectors such as norm
         weights); matrices are converted to the compute dtype."""
         return False
+
+    def norm_like(self, name: str) -> bool:
+        """True for tensors that random weights should draw around one instead of around zero (norm weights)."""
+        return self.keeps_dtype(name)
 
     def streams_first(self, rows: int) -> Optional[torch.Tensor]:
         """The weights that ``forward`` on ``rows`` rows reads first, if it streams them from memory once
@@ -142,10 +158,23 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedder(Part):
+    """Turns the step's tokens into rows of the fp32 residual stream. ``table`` is the [vocab, hidden] matrix that a
+    tied LM head shares."""
+    table: Optional[torch.Tensor] = None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, ctx, out: torch.Tensor, state: Optional[torch.Tensor]) -> None:
+        raise NotImplementedError
+
+
 _MIXERS: Dict[str, Callable] = {}
 _FEED_FORWARDS: Dict[str, Callable] = {}
 _NORMS: Dict[str, Callable] = {}
 _POSITIONS: Dict[str, Callable] = {}
+_EMBEDDERS: Dict[str, Callable] = {}
 
 
 def _register(table: Dict[str, Callable], what: str):
@@ -167,6 +196,8 @@ register_mixer = _register(_MIXERS, "mixer")
 register_feed_forward = _register(_FEED_FORWARDS, "feed-forward")
 register_norm = _register(_NORMS, "norm")
 register_position = _register(_POSITIONS, "position encoding")
+register_embedder = _register(_EMBEDDERS, "embedder")
+embedder_class = _lookup(_EMBEDDERS, "embedder")
 mixer_class = _lookup(_MIXERS, "mixer")
 feed_forward_class = _lookup(_FEED_FORWARDS, "feed-forward")
 norm_class = _lookup(_NORMS, "norm")

@@ -8,6 +8,7 @@ kernel), and returns its own pending delta, which the block after it (or the fin
 
 The built-in "pre_norm" is the reference's block (src/source/model/llama3.cpp:996-1181):
     h += delta_in;  x = norm1(h);  a = mixer(x);  h += a;  x = norm2(h);  return ffn(x)
+(a block whose spec has no feed-forward ends after the mixer and returns ``a``).
 Another arrangement (post-norm, parallel mixer and feed-forward, ...) is added with
 ``register_arrangement`` and needs no change here.
 """
@@ -39,8 +40,8 @@ def arrangement(name: str) -> Callable:
 
 
 class Block:
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm, arrangement_name: str = "pre_norm"):
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm,
+                 feed_forward_norm: Optional[Norm], arrangement_name: str = "pre_norm"):
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
@@ -71,6 +72,8 @@ def pre_norm(block: Block, resid, delta, ctx, cache):
         a = block.mixer.forward(x, ctx, cache, resid=resid)
     else:
         a = block.mixer.forward(x, ctx, cache)
+    if block.feed_forward is None:                        # a block of the mixer's sublayer alone
+        return a
     block.norm(block.feed_forward_norm, resid, a, x, block.feed_forward.streams_first(T))
     if block.feed_forward.adds_into_residual:
         return block.feed_forward.forward(x, ctx, resid=resid)

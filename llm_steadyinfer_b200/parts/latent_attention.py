@@ -1,0 +1,123 @@
+"""Latent attention mixer: queries, keys and values go through low-rank latents, and the cache keeps only the
+key/value latent and one rotated key part that all heads share.
+
+Per row h_t, with H heads, per head ``dq`` plain and ``dr`` rotated query/key entries, value size ``dv``, latent
+sizes ``q_rank`` and ``rk``:
+    c_q = norm(W_dq h) * g_q                         q = W_uq c_q        laid out head by head as [dq plain | dr rotated]
+    [l | r] = W_dkv h   (rk + dr rows)               c = norm(l) * g_kv        k_rot = rotate(r)   (one for all heads)
+    key of head i at position j:    [W_uk,i c_j | k_rot_j]          value: W_uv,i c_j
+    s_ij = scale * (q_plain,i . W_uk,i c_j + rotate(q_rot,i) . k_rot_j);   softmax over j <= t with exp(sink_i) once more
+    in the denominator;   out = W_o [heads' sums of p_j W_uv,i c_j]
+The up-projections of keys and values are never applied to the cache. Instead they move to the query side and
+behind the attention ("absorbed"): q_lat,i = W_uk,i^T q_plain,i scores against c_j directly, and
+sum_j p_j W_uv,i c_j = W_uv,i (sum_j p_j c_j). Attention then runs with one shared key "head" [c | k_rot] of rk + dr
+entries whose first rk entries also serve as the value, for prompts and decoding alike, so a page holds
+(rk + dr) numbers a token whatever the head count.
+
+Tensor names below the part's prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, sink, o.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import CacheNeed, Mixer, register_mixer
+from .linear import linear
+from .rotary import rotary_inverse_frequencies
+
+
+class LatentAttention(Mixer):
+    capturable = True
+
+    def __init__(self, params, dtype, device, position=None):
+        super().__init__(params, dtype, device, position)
+        g = params
+        self.hidden = int(g["hidden_size"])
+        self.H = int(g["num_heads"])
+        self.dq = int(g["head_dim"])             # plain (unrotated) part of a query/key head
+        self.dr = int(g["rot_dim"])              # rotated part
+        self.dv = int(g["value_dim"])
+        self.rk = int(g["kv_rank"])
+        self.q_rank = int(g["q_rank"])
+        self.scale = float(g["scale"])
+        self.eps = float(g["eps"])
+        self.rot_dims = int(g.get("rot_dims", self.dr))       # how many of the dr entries are rotated
+        self.window = g.get("window") or None
+        self.has_sink = bool(g.get("sink", True))
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.dr:
+            raise ValueError(f"latent_attention: rot_dims {self.rot_dims} must be even and at most rot_dim {self.dr}")
+        if self.rk + self.dr > 640:
+            raise ValueError(f"latent_attention: kv_rank + rot_dim {self.rk + self.dr} above 640 is not supported")
+        self.inv_freq = rotary_inverse_frequencies(self.rot_dims, float(g["rot_base"]), None).to(device) \
+            if self.rot_dims else torch.zeros(0, dtype=torch.float32, device=device)
+        self.down = self.uq = self.ukT = self.uv = self.o = None
+        self.q_norm = self.kv_norm = self.sink = None
+
+    def weight_shapes(self):
+        H = self.H
+        shapes = {"dq": (self.q_rank, self.hidden), "dq.norm": (self.q_rank,),
+                  "uq": (H * (self.dq + self.dr), self.q_rank),
+                  "dkv": (self.rk + self.dr, self.hidden), "dkv.norm": (self.rk,),
+                  "uk": (H * self.dq, self.rk), "uv": (H * self.dv, self.rk),
+                  "o": (self.hidden, H * self.dv)}
+        if self.has_sink:
+            shapes["sink"] = (H,)
+        return shapes
+
+    def keeps_dtype(self, name):
+        return name in ("dq.norm", "dkv.norm", "sink")
+
+    def norm_like(self, name):
+        return name in ("dq.norm", "dkv.norm")
+
+    def load_weights(self, t):
+        H = self.H
+        self.down = torch.cat([t["dq"], t["dkv"]], 0).contiguous()          # one product for both latents
+        self.uq = t["uq"].contiguous()
+        # per head the key up-projection transposed, [rk, dq]: q_lat = q_plain @ W_uk,i as a product with rows of W^T
+        self.ukT = t["uk"].view(H, self.dq, self.rk).transpose(1, 2).contiguous()
+        self.uv = t["uv"].view(H, self.dv, self.rk).contiguous()
+        self.o = t["o"].contiguous()
+        self.q_norm = t["dq.norm"].contiguous()
+        self.kv_norm = t["dkv.norm"].float().contiguous()
+        self.sink = t["sink"].float().contiguous() if self.has_sink else None
+
+    def cache_need(self):
+        return CacheNeed(1, self.rk + self.dr, self.window, 0)
+
+    def streams_first(self, rows):
+        return self.down if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
+
+    def kernel_files(self, page_size):
+        names = ("attention_general", "norm")
+        return names + (("gemm_f32",) if self.dtype == torch.float32 else ("gemm_skinny", "gemm_rows", "gemm_tc05"))
+
+    def forward(self, x, ctx, cache):
+        T = x.shape[0]
+        H, dq, dr, dv, rk = self.H, self.dq, self.dr, self.dv, self.rk
+        lat = ctx.buf("lat_down", (T, self.q_rank + rk + dr), self.dtype)
+        linear(x, self.down, lat, ctx.status)
+        cq = ctx.buf("lat_cq", (T, self.q_rank), self.dtype)
+        ops.rmsnorm_rows(lat[:, :self.q_rank], self.q_norm, self.eps, cq)
+        q = ctx.buf("lat_q", (T, H * (dq + dr)), self.dtype)
+        linear(cq, self.uq, q, ctx.status)
+        # queries against the cached latents: [W_uk,i^T q_plain,i | rotated part] per head
+        q_full = ctx.buf("lat_qfull", (T, H * (rk + dr)), self.dtype)
+        for i in range(H):
+            linear(q[:, i * (dq + dr): i * (dq + dr) + dq], self.ukT[i], q_full[:, i * (rk + dr): i * (rk + dr) + rk], ctx.status)
+        ops.latent_prepare(lat[:, self.q_rank:], q, q_full, self.kv_norm, self.eps, self.inv_freq, self.rot_dims,
+                           ctx.positions, ctx.row_seq, cache.block_table, cache.k if cache.writes else None,
+                           cache.page_size, ctx.seq_slots, H, dq, dr, rk, status=ctx.status)
+        o_lat = ctx.buf("lat_olat", (T, H * rk), self.dtype)
+        ops.attention_general(q_full, cache.k, None, cache.block_table, ctx.row_seq, ctx.positions, o_lat, cache.page_size,
+                              ctx.seq_slots, H, 1, rk + dr, rk, self.scale, self.window or 0, sink=self.sink,
+                              status=ctx.status)
+        attn = ctx.buf("attn_out", (T, H * dv), self.dtype)
+        for i in range(H):
+            linear(o_lat[:, i * rk:(i + 1) * rk], self.uv[i], attn[:, i * dv:(i + 1) * dv], ctx.status)
+        out = ctx.buf("delta", (T, self.hidden), self.dtype)
+        linear(attn, self.o, out, ctx.status)
+        return out
+
+
+register_mixer("latent_attention", LatentAttention)

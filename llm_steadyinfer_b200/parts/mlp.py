@@ -81,3 +81,46 @@ class GatedMLP(FeedForward):
 
 
 register_feed_forward("gated_mlp", GatedMLP)
+
+
+class DenseMLP(FeedForward):
+    """Feed-forward without a gate: ``down(act(up(x)))``; ``activation`` is one of ``ops.ACTIVATIONS`` ("relu2": the
+    square of relu). Tensor names are parameters (``up_name``, ``down_name``)."""
+    capturable = True
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = params.get("activation", "relu2")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_mlp: activation {self.activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
+        self.up_name = params.get("up_name", "up_proj.weight")
+        self.down_name = params.get("down_name", "down_proj.weight")
+        self.up = None
+        self.down = None
+
+    def weight_shapes(self):
+        return {self.up_name: (self.inter, self.hidden), self.down_name: (self.hidden, self.inter)}
+
+    def load_weights(self, tensors):
+        self.up = tensors[self.up_name].contiguous()
+        self.down = tensors[self.down_name].contiguous()
+
+    def streams_first(self, rows):
+        return self.up if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
+
+    def kernel_files(self, page_size):
+        return ("gemm_f32", "activation") if self.dtype == torch.float32 else ("gemm_skinny", "gemm_tc05", "gemm_rows", "activation")
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        act = ctx.buf("ffn_act", (T, self.inter), self.dtype)
+        linear(x, self.up, act, ctx.status)
+        ops.activation(act, act, self.activation)
+        out = ctx.buf("delta", (T, self.hidden), self.dtype)
+        linear(act, self.down, out, ctx.status)
+        return out
+
+
+register_feed_forward("dense_mlp", DenseMLP)

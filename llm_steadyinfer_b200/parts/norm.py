@@ -21,16 +21,17 @@ class RMSNorm(Norm):
         super().__init__(params, dtype, device)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.name = params.get("weight_name", "weight")      # "" where the checkpoint names the vector by the prefix alone
         self.weight: Optional[torch.Tensor] = None
 
     def weight_shapes(self):
-        return {"weight": (self.size,)}
+        return {self.name: (self.size,)}
 
     def keeps_dtype(self, name: str) -> bool:
         return True
 
     def load_weights(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.name].contiguous()
 
     def kernel_files(self, page_size):
         return ("norm",)

@@ -43,7 +43,10 @@ def checkpoint_files(model_dir: str) -> List[str]:
 def check_names_and_shapes(wanted: Dict[str, tuple], found: Dict[str, tuple], optional=()) -> None:
     missing = sorted(n for n in wanted if n not in found)
     unexpected = sorted(n for n in found if n not in wanted and n not in optional)
-    wrong = sorted((n, wanted[n], found[n]) for n in wanted if n in found and tuple(found[n]) != tuple(wanted[n]))
+    def fits(want, got):             # -1 in a wanted shape: the checkpoint decides that size
+        return len(want) == len(got) and all(w == -1 or w == g for w, g in zip(want, got))
+
+    wrong = sorted((n, wanted[n], found[n]) for n in wanted if n in found and not fits(tuple(wanted[n]), tuple(found[n])))
     if not (missing or unexpected or wrong):
         return
     lines = ["checkpoint does not match the model:"]

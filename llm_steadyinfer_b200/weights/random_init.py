@@ -74,7 +74,9 @@ def _draw(name: str, shape, is_norm: bool, seed: int, device, store_dtype: torch
 def random_tensors(model, seed: int, store_dtype: torch.dtype, device="cpu") -> Dict[str, torch.Tensor]:
     out = {}
     for name, shape in sorted(model.weight_shapes().items()):
-        out[name] = _draw(name, shape, model.keeps_dtype(name), seed, device, store_dtype)
+        if any(s < 0 for s in shape):
+            raise ValueError(f"random weights: the configuration leaves the shape of {name!r} to the checkpoint {list(shape)}")
+        out[name] = _draw(name, shape, model.norm_like(name), seed, device, store_dtype)
     return out
 
 
@@ -98,6 +100,6 @@ def init_random(model, seed: int, store_dtype: torch.dtype = torch.bfloat16) -> 
     checkpoint would be."""
     tensors = {}
     for name, shape in sorted(model.weight_shapes().items()):
-        t = _draw(name, shape, model.keeps_dtype(name), seed, model.device, store_dtype)
+        t = _draw(name, shape, model.norm_like(name), seed, model.device, store_dtype)
         tensors[name] = place(t, model.keeps_dtype(name), model.dtype, model.device)
     model.load_weights(tensors)
