@@ -217,8 +217,11 @@ def forward(cfg, w, tokens, return_layers=False):
     """Logits [T, vocab] (float64) of one whole sequence; with ``return_layers`` also the residual stream
     after every layer run [runs, T, width]."""
     eps = cfg["norm"]["eps"]
-    bg = cfg["embedding"]["bigram"]
-    x = embed_tokens(list(tokens), w["embed"], w["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    if bg is None:
+        x = torch.stack([w["embed"][t] for t in tokens])
+    else:
+        x = embed_tokens(list(tokens), w["embed"], w["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
     layers = []
     for i, layer in enumerate(cfg["layers"]):
         src = layer.get("weights_of", i)

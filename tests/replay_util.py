@@ -130,14 +130,15 @@ def replay_in_process(replayer, steps: List[dict]):
 class PlainLogits:
     """Whole-sequence logits of the plain implementation, computed once per request."""
 
-    def __init__(self, model_dir: str):
-        self.cfg, self.w = plain_llama.read_model_folder(model_dir)
+    def __init__(self, model_dir: str, plain=plain_llama):
+        self.plain = plain
+        self.cfg, self.w = plain.read_model_folder(model_dir)
         self._cache: Dict[tuple, torch.Tensor] = {}
 
     def of(self, tokens: Sequence[int]) -> torch.Tensor:
         key = tuple(tokens)
         if key not in self._cache:
-            self._cache[key] = plain_llama.forward(self.cfg, self.w, tokens)
+            self._cache[key] = self.plain.forward(self.cfg, self.w, tokens)
         return self._cache[key]
 
 
