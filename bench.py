@@ -229,6 +229,135 @@ def reference_arm(args) -> int:
     return 0
 
 
+# ---- the Mivorax design beside the closest existing model ---------------------------------------------------
+MIVORAX_WIDTH, MIVORAX_FF, MIVORAX_VOCAB = 2048, 5632, 32000
+_LATENT = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 512, "scale": 192 ** -0.5,
+           "rot": {"base": 10000.0, "dims": 64}}
+_BIASED = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "bias_max": 4096.0, "bias_buckets": 64}
+_SSM = {"heads": 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+
+
+def _mivorax_config():
+    dense = {"kind": "dense", "ff": MIVORAX_FF}
+    one = [{"type": "latent_attention", "mixer": _LATENT, "mlp": dense}, {"type": "attention", "mixer": _BIASED, "mlp": dense},
+           {"type": "attention", "mixer": _BIASED, "mlp": dense}, {"type": "mamba2", "mixer": _SSM, "mlp": None}]
+    return {"architecture": "Mivorax", "vocab": MIVORAX_VOCAB, "width": MIVORAX_WIDTH, "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": one + one}
+
+
+def _llama_twin():
+    d = dict(LLAMA_3_1_8B)
+    d.update(hidden_size=MIVORAX_WIDTH, intermediate_size=MIVORAX_FF, num_hidden_layers=8, num_attention_heads=16,
+             num_key_value_heads=4, head_dim=128, vocab_size=MIVORAX_VOCAB)
+    return d
+
+
+def mivorax_section(args) -> int:
+    """Prefill of 2,048 tokens and decode (batch 8, context 4,096) of an 8-layer Mivorax model (2 latent attention,
+    4 attention with distance bias, 2 state-space layers; width 2,048) and of a Llama model of the same width, depth,
+    heads and vocabulary; random weights, bf16. Per model: milliseconds per step, tokens/s, and the device time per
+    kind of kernel of one direct step (events between the kernels: compare kinds, not sums)."""
+    import torch
+    from llm_steadyinfer_b200.config import config_from_dict
+    from llm_steadyinfer_b200.engine.kernel_times import KernelTimes
+    from llm_steadyinfer_b200.engine.step import ModelRunner, StepEntry
+    from llm_steadyinfer_b200.models import Model
+    from llm_steadyinfer_b200.weights import init_random
+
+    torch.cuda.set_device(0)
+    PT, B, CTX, PAGE = 2048, args.batch, min(args.context, 4096), 16
+    K, W = min(args.steps, 32), max(3, min(args.warmup, 8))
+    gen = torch.Generator().manual_seed(1)
+    rand_tokens = lambda n: torch.randint(0, MIVORAX_VOCAB, (n,), generator=gen).tolist()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")        # larger than L2: written between timed steps
+    results = {}
+    for name, cfg_d in (("mivorax", _mivorax_config()), ("llama", _llama_twin())):
+        model = Model(config_from_dict(cfg_d), torch.bfloat16, "cuda:0")
+        init_random(model, seed=0)
+        runner = ModelRunner(model, page_size=PAGE, num_pages=(B * CTX + PT) // PAGE + 8, max_requests=max(B, 2),
+                             max_step_tokens=PT + B, max_seq_len=CTX)
+        mgr = runner.manager
+        for t in runner.storage.keys + runner.storage.values:
+            if t is not None:
+                t.normal_(0.0, 0.5)
+        ptoks = rand_tokens(PT)
+
+        def prefill(_):
+            runner.step([StepEntry("p", ptoks, [PT - 1])])
+            runner.finish("p")
+
+        def timed_each(fn, n):
+            out = []
+            for i in range(n):
+                flush.zero_()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); fn(i); b.record()
+                torch.cuda.synchronize()
+                out.append(a.elapsed_time(b))
+            return statistics.median(out)
+
+        for i in range(3):
+            prefill(i)
+        runner.check_status()
+        pre_ms = timed_each(prefill, 5)
+        with KernelTimes() as kt:
+            prefill(0)
+        pre_kinds = {k: v["ms"] for k, v in kt.report().items()}
+        ids = [f"d{i}" for i in range(B)]
+        start = CTX - (K + W) - 2
+        for r in ids:
+            mgr.admit(r); mgr.grow(r, start); mgr.commit(r, start)
+        runner.storage.zero_new_slots()
+        toks = [rand_tokens(B) for _ in range(K + W + 1)]
+        state = {"i": 0}
+
+        def decode(_):
+            entries = [StepEntry(r, [toks[state["i"]][j]], [0]) for j, r in enumerate(ids)]
+            state["i"] += 1
+            if runner.graphs_available():
+                runner.step_decode_graph(entries)
+            else:
+                runner.step(entries)
+
+        for i in range(W):
+            decode(i)
+        runner.check_status()
+        dec_ms = timed_each(decode, K)
+        with KernelTimes() as kt:
+            entries = [StepEntry(r, [toks[state["i"]][j]], [0]) for j, r in enumerate(ids)]
+            runner.step(entries)
+        dec_kinds = {k: v["ms"] for k, v in kt.report().items()}
+        runner.check_status()
+        results[name] = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(PT / pre_ms * 1e3, 1),
+                         "decode_ms_per_step": round(dec_ms, 4), "decode_tokens_per_s": round(B / dec_ms * 1e3, 1),
+                         "graphs": runner.graphs_available(), "launches_per_decode_step": runner.launches_last_step,
+                         "prefill_kernel_ms": pre_kinds, "decode_kernel_ms": dec_kinds,
+                         "weight_bytes": sum(t.numel() * t.element_size() for t in _model_tensors(model))}
+        del runner, model
+        torch.cuda.empty_cache()
+    pk, pk_src = peaks()
+    print(json.dumps({"section": "mivorax", "dtype": "bf16", "data": "synthetic: random weights (seed 0), random token ids",
+                      "config": {"width": MIVORAX_WIDTH, "layers": 8, "ff": MIVORAX_FF, "vocab": MIVORAX_VOCAB, "prefill_tokens": PT,
+                                 "decode_batch": B, "decode_context": CTX, "page_size": PAGE, "l2": "256 MB written between timed steps",
+                                 "latent": _LATENT, "attention": _BIASED, "state_space": _SSM},
+                      "peaks": pk, "peaks_source": pk_src, "models": results}))
+    return 0
+
+
+def _model_tensors(model):
+    seen, out = set(), []
+    for _, part in model._named_parts():
+        for v in vars(part).values():
+            ts = v if isinstance(v, (list, tuple)) else [v]
+            for t in ts:
+                if hasattr(t, "data_ptr") and hasattr(t, "numel") and t.data_ptr() not in seen:
+                    seen.add(t.data_ptr()); out.append(t)
+    if model.lm_head is not None and model.lm_head.data_ptr() not in seen:
+        out.append(model.lm_head)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -244,8 +373,10 @@ def main() -> int:
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed region of --section with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off)")
-    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill"],
-                    help="run only the device-timed decode steps or only the prefill (for profiling)")
+    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill", "mivorax"],
+                    help="run only the device-timed decode steps or only the prefill (for profiling); 'mivorax': prefill "
+                         "and decode of a Mivorax model at layer sizes of a real model beside a Llama model of equal "
+                         "width, with time per kind of kernel (its own JSON line; the default workload is not run)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -254,6 +385,8 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     K, W = args.steps, max(3, args.warmup)
+    if args.section == "mivorax":
+        return mivorax_section(args)
 
     import torch
     from llm_steadyinfer_b200 import LLM, SamplingParams

@@ -1,0 +1,374 @@
+// bf16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, fp32 accumulation, fp32 online
+// softmax) in the general form of attention_general.cu: key size dk and value size dv of any multiple of 8,
+// values of their own or the first dv entries of the keys (a latent that is key and value), a bias by distance
+// added to the scaled score, a sink per head in the denominator. One kernel serves prompt portions and decode
+// rows; for decode the key range of an item can be split over blocks, whose fp32 partial results a second small
+// kernel merges.
+//
+// A work item is a run of consecutive query tokens of one sequence. A block handles one item, one KV head, one
+// part of that KV head's query heads (Gb of them, so that tokens * Gb rows fit the 64-row tile; a latent shared
+// by 128 heads is served in two parts), one slice of DVB value columns and one share of the keys. Row r of the
+// tile is token r / Gb, head r % Gb; warp w owns rows 16w..16w+15 and walks all keys of the share. K tiles of
+// BLOCK_N keys x dk come through cp.async into XOR-swizzled shared memory, two stages deep; the values are a
+// second tile (own values: only the block's slice) or columns of the key tile itself.
+// Sizes are run-time values: the loops over dk are not unrolled by the compiler, only the value slice (DVB, the
+// accumulators) and the key tile (BLOCK_N) are template parameters.
+#include "attention_common.cuh"
+
+struct FlexParams {
+  const bf16* q; long long q_stride;
+  const bf16* k_cache; const bf16* v_cache;      // v_cache nullptr: values are keys[..., :dv]
+  const int* block_table; int table_width;
+  const AttnItem* items; int num_items;
+  bf16* out; long long out_stride;
+  float* part_o;            // [item][gy][split][64 rows][dv]   (nsplit > 1)
+  float* part_ml;           // [item][gy][split][64 rows][2]
+  const float* dist_bias; int nd;                // fp32 [nd, H] or nullptr
+  const float* sink;                             // fp32 [H] or nullptr
+  int num_pages, page_size, num_seqs, H, KV, G, Gb, hparts, dk, dv, dk_pitch;
+  float scale_log2;         // scale * log2(e)
+  int window, nsplit;
+  int* status;
+};
+
+#define FLEX_M 64
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ bf16* ftile(bf16* base, int pitch_chunks, int row, int chunk) {
+  return base + ((size_t)row * pitch_chunks + (chunk ^ (row & 7))) * 8;
+}
+
+template <int BLOCK_N, int DVB>
+__global__ void __launch_bounds__(128)
+attn_flex_kernel(const FlexParams p) {
+  constexpr int THREADS = 128;
+  constexpr int NT = BLOCK_N / 8;
+  constexpr int DT = DVB / 8;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int kch = p.dk_pitch / 8;                       // 16-byte chunks of a key row in shared memory
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+  bf16* Ks = Qs + (size_t)FLEX_M * p.dk_pitch;          // [2][BLOCK_N][dk_pitch]
+  bf16* Vs = Ks + (size_t)2 * BLOCK_N * p.dk_pitch;     // [2][BLOCK_N][DVB]  (own values only)
+  const bool own_v = p.v_cache != nullptr;
+
+  const int item_idx = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
+  const AttnItem item = p.items[item_idx];
+  const int g = blockIdx.y / p.hparts, hpart = blockIdx.y % p.hparts;
+  const int v0 = blockIdx.z * DVB;                      // first value column of this block
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (item.ntok <= 0) return;
+  if (item.seq < 0 || item.seq >= p.num_seqs) {
+    if (threadIdx.x == 0) set_status(p.status, SI_BAD_SEQ);
+    return;
+  }
+  const int* table = p.block_table + (size_t)item.seq * p.table_width;
+  const int kv_end_all = item.pos0 + item.ntok;
+  const int kv_lo = window_first_key(item.pos0, p.window);
+  const int kv_begin_all = kv_lo / BLOCK_N * BLOCK_N;
+  const int tiles_all = (kv_end_all - kv_begin_all + BLOCK_N - 1) / BLOCK_N;
+  const int tiles_per = (tiles_all + p.nsplit - 1) / p.nsplit;
+  const int t_begin = split * tiles_per;
+  const int t_end = min(tiles_all, t_begin + tiles_per);
+  const int ntiles = max(0, t_end - t_begin);
+  const int kv_begin = kv_begin_all + t_begin * BLOCK_N;
+  const int kv_end = min(kv_end_all, kv_begin_all + t_end * BLOCK_N);
+  const int head0 = g * p.G + hpart * p.Gb;
+  const int dk_chunks = p.dk / 8;
+  const int kt_steps = (p.dk + 15) / 16;
+
+  auto load_kv = [&](int j0, int stage) {
+    bf16* Kt = Ks + (size_t)stage * BLOCK_N * p.dk_pitch;
+    for (int id = threadIdx.x; id < BLOCK_N * kch; id += THREADS) {
+      const int row = id / kch, c = id % kch;
+      const int j = j0 + row;
+      bool valid = j >= kv_lo && j < kv_end && c < dk_chunks;
+      size_t off = 0;
+      if (valid) {
+        const int slot = j / p.page_size;
+        const int page = slot < p.table_width ? table[slot] : -1;
+        if (page < 0 || page >= p.num_pages) {
+          set_status(p.status, SI_BAD_PAGE);
+          valid = false;
+        } else {
+          off = (((size_t)page * p.KV + g) * p.page_size + (j - slot * p.page_size)) * p.dk + c * 8;
+        }
+      }
+      cp_async16(ftile(Kt, kch, row, c), p.k_cache + off, valid);
+    }
+    if (own_v) {
+      bf16* Vt = Vs + (size_t)stage * BLOCK_N * DVB;
+      for (int id = threadIdx.x; id < BLOCK_N * DT; id += THREADS) {
+        const int row = id / DT, c = id % DT;
+        const int j = j0 + row;
+        bool valid = j >= kv_lo && j < kv_end && v0 + c * 8 < p.dv;
+        size_t off = 0;
+        if (valid) {
+          const int slot = j / p.page_size;
+          const int page = slot < p.table_width ? table[slot] : -1;
+          if (page < 0 || page >= p.num_pages) valid = false;
+          else off = (((size_t)page * p.KV + g) * p.page_size + (j - slot * p.page_size)) * p.dv + v0 + c * 8;
+        }
+        cp_async16(ftile(Vt, DT, row, c), p.v_cache + off, valid);
+      }
+    }
+  };
+
+  if (ntiles > 0) {
+    for (int id = threadIdx.x; id < FLEX_M * kch; id += THREADS) {
+      const int row = id / kch, c = id % kch;
+      const int tok = row / p.Gb, hh = row - tok * p.Gb;
+      const bool valid = tok < item.ntok && c < dk_chunks;
+      const bf16* src = p.q;
+      if (valid) src = p.q + (size_t)(item.row0 + tok) * p.q_stride + (size_t)(head0 + hh) * p.dk + c * 8;
+      cp_async16(ftile(Qs, kch, row, c), src, valid);
+    }
+    load_kv(kv_begin, 0);
+  }
+  cp_async_commit();
+
+  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const int tok_lo = r_lo / p.Gb, tok_hi = r_hi / p.Gb;
+  const int pos_lo = tok_lo < item.ntok ? item.pos0 + tok_lo : -1;     // -1: row unused
+  const int pos_hi = tok_hi < item.ntok ? item.pos0 + tok_hi : -1;
+  const int head_lo = head0 + r_lo % p.Gb, head_hi = head0 + r_hi % p.Gb;
+  const int warp_last_tok = min(item.ntok - 1, (warp * 16 + 15) / p.Gb);
+  const int warp_first_tok = (warp * 16) / p.Gb;
+  const bool warp_active = warp_first_tok < item.ntok;
+  const int warp_max_pos = item.pos0 + warp_last_tok;
+  const int warp_min_pos = item.pos0 + warp_first_tok;
+
+  float o[DT][4];
+#pragma unroll
+  for (int i = 0; i < DT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int j0 = kv_begin + t * BLOCK_N;
+    bf16* Kt = Ks + (size_t)(t & 1) * BLOCK_N * p.dk_pitch;
+    if (t + 1 < ntiles) {
+      load_kv(j0 + BLOCK_N, (t + 1) & 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    bool skip = !warp_active || j0 > warp_max_pos;
+    if (p.window > 0 && j0 + BLOCK_N - 1 <= warp_min_pos - p.window) skip = true;
+    if (!skip) {
+      float s[NT][4];
+#pragma unroll
+      for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll 2
+      for (int kk = 0; kk < kt_steps; ++kk) {
+        unsigned a0, a1, a2, a3;
+        ldsm_x4(a0, a1, a2, a3, ftile(Qs, kch, warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+          unsigned b0, b1, b2, b3;
+          ldsm_x4(b0, b1, b2, b3, ftile(Kt, kch, nt * 8 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+          mma_bf16(s[nt], a0, a1, a2, a3, b0, b1);
+          mma_bf16(s[nt + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      float mx_lo = m_lo, mx_hi = m_hi;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const int pos = (e < 2) ? pos_lo : pos_hi;
+          const bool vis = j >= kv_lo && j <= pos && (p.window <= 0 || j > pos - p.window);
+          float v = -INFINITY;
+          if (vis) {
+            v = s[nt][e] * p.scale_log2;
+            if (p.dist_bias) v += p.dist_bias[(size_t)min(pos - j, p.nd - 1) * p.H + ((e < 2) ? head_lo : head_hi)] * LOG2E;
+          }
+          s[nt][e] = v;
+          if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float base_lo = mx_lo == -INFINITY ? 0.f : mx_lo;
+      const float base_hi = mx_hi == -INFINITY ? 0.f : mx_hi;
+      const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
+      m_lo = mx_lo; m_hi = mx_hi;
+      float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        s[nt][0] = exp2f(s[nt][0] - base_lo); s[nt][1] = exp2f(s[nt][1] - base_lo);
+        s[nt][2] = exp2f(s[nt][2] - base_hi); s[nt][3] = exp2f(s[nt][3] - base_hi);
+        sum_lo += s[nt][0] + s[nt][1];
+        sum_hi += s[nt][2] + s[nt][3];
+      }
+      l_lo = l_lo * corr_lo + sum_lo;
+      l_hi = l_hi * corr_hi + sum_hi;
+#pragma unroll
+      for (int i = 0; i < DT; ++i) {
+        o[i][0] *= corr_lo; o[i][1] *= corr_lo; o[i][2] *= corr_hi; o[i][3] *= corr_hi;
+      }
+      // O += P V: own values from their tile, else columns v0.. of the key tile
+      bf16* Vt = own_v ? Vs + (size_t)(t & 1) * BLOCK_N * DVB : Kt;
+      const int vch = own_v ? DT : kch;
+      const int vc0 = own_v ? 0 : v0 / 8;
+#pragma unroll
+      for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+        const unsigned a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        const unsigned a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        const unsigned a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        const unsigned a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dt = 0; dt < DT; dt += 2) {
+          if (v0 + dt * 8 >= p.dv) break;                 // columns beyond the values: nothing there to read
+          unsigned b0, b1, b2, b3;
+          ldsm_x4_t(b0, b1, b2, b3, ftile(Vt, vch, kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), vc0 + dt + (lane >> 4)));
+          mma_bf16(o[dt], a0, a1, a2, a3, b0, b1);
+          mma_bf16(o[dt + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+    __syncthreads();       // everyone is done with this stage before it is refilled
+  }
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+  if (p.nsplit > 1) {                       // partial results: unnormalised sums, maximum (base 2) and denominator
+    const size_t slab = ((size_t)item_idx * gridDim.y + blockIdx.y) * p.nsplit + split;
+    float* po = p.part_o + slab * FLEX_M * p.dv;
+    float* pml = p.part_ml + slab * FLEX_M * 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = half ? r_hi : r_lo;
+      if (r / p.Gb >= item.ntok) continue;
+      if ((lane & 3) == 0 && blockIdx.z == 0) {
+        pml[r * 2] = half ? m_hi : m_lo;
+        pml[r * 2 + 1] = half ? l_hi : l_lo;
+      }
+#pragma unroll
+      for (int dt = 0; dt < DT; ++dt) {
+        const int d = v0 + dt * 8 + (lane & 3) * 2;
+        if (d < p.dv) *reinterpret_cast<float2*>(po + (size_t)r * p.dv + d) = make_float2(o[dt][half * 2], o[dt][half * 2 + 1]);
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? r_hi : r_lo;
+    const int tok = r / p.Gb, hh = r - tok * p.Gb;
+    if (tok >= item.ntok) continue;
+    float l = half ? l_hi : l_lo, f = 1.f;
+    if (p.sink) {                           // exp(sink) joins the denominator once
+      const float m = half ? m_hi : m_lo, s2 = p.sink[head0 + hh] * LOG2E;
+      const float M = fmaxf(m, s2);
+      f = exp2f(m - M);
+      l = l * f + exp2f(s2 - M);
+    }
+    const float inv = l > 0.f ? f / l : 0.f;
+    bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(head0 + hh) * p.dv;
+#pragma unroll
+    for (int dt = 0; dt < DT; ++dt) {
+      const int d = v0 + dt * 8 + (lane & 3) * 2;
+      if (d < p.dv)
+        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
+    }
+  }
+}
+
+// Merge of the shares of split items: one block per (item, gy), a thread per (row, value column).
+__global__ void attn_flex_merge_kernel(const FlexParams p) {
+  pdl_prologue();
+  const AttnItem item = p.items[blockIdx.x];
+  if (item.ntok <= 0 || item.seq < 0 || item.seq >= p.num_seqs) return;
+  const int g = blockIdx.y / p.hparts, hpart = blockIdx.y % p.hparts;
+  const int head0 = g * p.G + hpart * p.Gb;
+  const size_t slab0 = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit;
+  const int rows = item.ntok * p.Gb;
+  for (int idx = threadIdx.x; idx < rows * p.dv; idx += blockDim.x) {
+    const int r = idx / p.dv, d = idx % p.dv;
+    const int tok = r / p.Gb, hh = r - tok * p.Gb;
+    float M = p.sink ? p.sink[head0 + hh] * LOG2E : -INFINITY;
+    for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, p.part_ml[((slab0 + s) * FLEX_M + r) * 2]);
+    float L = p.sink ? exp2f(p.sink[head0 + hh] * LOG2E - M) : 0.f, acc = 0.f;
+    for (int s = 0; s < p.nsplit; ++s) {
+      const float m = p.part_ml[((slab0 + s) * FLEX_M + r) * 2];
+      if (m == -INFINITY) continue;                         // a share without keys
+      const float w = exp2f(m - M);
+      L += p.part_ml[((slab0 + s) * FLEX_M + r) * 2 + 1] * w;
+      acc += p.part_o[((slab0 + s) * FLEX_M + r) * p.dv + d] * w;
+    }
+    p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(head0 + hh) * p.dv + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+static int flex_heads_per_block(int G) {          // the largest divisor of G that fits the 64-row tile
+  for (int gb = G < FLEX_M ? G : FLEX_M; gb >= 1; --gb)
+    if (G % gb == 0) return gb;
+  return 1;
+}
+
+SI_EXPORT int si_attn_flex_ok(int H, int KV, int dk, int dv, int own_v) {
+  if (H <= 0 || KV <= 0 || H % KV || dk <= 0 || dv <= 0 || dk % 8 || dv % 8 || dk > 640) return 0;
+  if (!own_v && dv > dk) return 0;
+  return 1;
+}
+// Most tokens of one item.
+SI_EXPORT int si_attn_flex_tokens(int H, int KV) { return FLEX_M / flex_heads_per_block(H / KV); }
+SI_EXPORT long long si_attn_flex_scratch_floats(int num_items, int H, int KV, int dv, int nsplit) {
+  const int G = H / KV, gy = KV * (G / flex_heads_per_block(G));
+  return (long long)num_items * gy * nsplit * FLEX_M * (dv + 2);
+}
+
+template <int BLOCK_N, int DVB>
+static int flex_launch(const FlexParams& p, int dslices, size_t smem, cudaStream_t stream) {
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    if (cudaFuncSetAttribute(attn_flex_kernel<BLOCK_N, DVB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return -2;
+    configured = smem;
+  }
+  attn_flex_kernel<BLOCK_N, DVB><<<dim3(p.num_items * p.nsplit, p.KV * p.hparts, dslices), 128, smem, stream>>>(p);
+  return 0;
+}
+
+SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                           const int* block_table, int table_width, const int* items, int num_items, void* out,
+                           long long out_stride, int num_pages, int page_size, int num_seqs, int H, int KV, int dk,
+                           int dv, float scale, int window, const float* dist_bias, int nd, const float* sink,
+                           int nsplit, float* scratch, int* status, cudaStream_t stream) {
+  if (num_items <= 0) return 0;
+  if (!si_attn_flex_ok(H, KV, dk, dv, v_cache != nullptr) || nsplit < 1 || (nsplit > 1 && !scratch)) return -2;
+  FlexParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.block_table = block_table; p.table_width = table_width;
+  p.items = (const AttnItem*)items; p.num_items = num_items;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.dist_bias = dist_bias; p.nd = nd; p.sink = sink;
+  p.num_pages = num_pages; p.page_size = page_size; p.num_seqs = num_seqs;
+  p.H = H; p.KV = KV; p.G = H / KV; p.Gb = flex_heads_per_block(p.G); p.hparts = p.G / p.Gb;
+  p.dk = dk; p.dv = dv; p.dk_pitch = (dk + 63) / 64 * 64;
+  p.scale_log2 = scale * LOG2E; p.window = window; p.nsplit = nsplit; p.status = status;
+  const long long slabs = (long long)num_items * KV * p.hparts * nsplit;
+  p.part_o = scratch;
+  p.part_ml = scratch ? scratch + slabs * FLEX_M * dv : nullptr;
+  const bool own_v = v_cache != nullptr;
+  const int block_n = p.dk_pitch > 256 ? 32 : 64;        // the two key stages and the queries share 227 KB
+  const int dvb = dv > 64 ? 128 : 64;
+  const int dslices = (dv + dvb - 1) / dvb;
+  const size_t smem = ((size_t)(FLEX_M + 2 * block_n) * p.dk_pitch + (own_v ? (size_t)2 * block_n * dvb : 0)) * sizeof(bf16);
+  if (smem > 227 * 1024) return -2;
+  int rc;
+  if (block_n == 64) rc = dvb == 128 ? flex_launch<64, 128>(p, dslices, smem, stream) : flex_launch<64, 64>(p, dslices, smem, stream);
+  else rc = dvb == 128 ? flex_launch<32, 128>(p, dslices, smem, stream) : flex_launch<32, 64>(p, dslices, smem, stream);
+  if (rc) return rc;
+  if (nsplit > 1) {
+    const int threads = 256;
+    attn_flex_merge_kernel<<<dim3(num_items, KV * p.hparts), threads, 0, stream>>>(p);
+  }
+  return si_last_error();
+}

@@ -980,3 +980,63 @@ def gated_part_norm(y, z, weight, out, parts: int, eps: float) -> None:
     f = _fn("ssm", "si_gated_part_norm", [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p])
     _check(f(_ptr(y), y.stride(0), _ptr(z), _dt(z), z.stride(0), _ptr(weight), _ptr(out), out.stride(0), T, W, int(parts),
              float(eps), _stream()), f"gated_part_norm(width={W}, parts={parts})")
+
+
+# ---- general attention on the tensor cores (bf16) ---------------------------------------------------------
+
+def attn_flex_ok(H: int, KV: int, dk: int, dv: int, own_v: bool) -> bool:
+    lib = build.load("attention_flex")
+    lib.si_attn_flex_ok.restype = _c_int
+    return bool(lib.si_attn_flex_ok(_c_int(H), _c_int(KV), _c_int(dk), _c_int(dv), _c_int(1 if own_v else 0)))
+
+
+def attn_flex_tokens(H: int, KV: int) -> int:
+    """Most tokens of one work item of ``attn_flex``."""
+    lib = build.load("attention_flex")
+    lib.si_attn_flex_tokens.restype = _c_int
+    return lib.si_attn_flex_tokens(_c_int(H), _c_int(KV))
+
+
+def attn_flex_scratch_floats(num_items: int, H: int, KV: int, dv: int, nsplit: int) -> int:
+    lib = build.load("attention_flex")
+    lib.si_attn_flex_scratch_floats.restype = _c_llr
+    return lib.si_attn_flex_scratch_floats(_c_int(num_items), _c_int(H), _c_int(KV), _c_int(dv), _c_int(nsplit))
+
+
+def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int, dk: int,
+              dv: int, scale: float, window: int = 0, dist_bias=None, sink=None, nsplit: int = 1, scratch=None,
+              status=None) -> None:
+    """``attention_general`` on the tensor cores for bfloat16. ``items``: int32 [n, 4] rows (sequence, first row,
+    tokens, first position) of at most ``attn_flex_tokens`` tokens. ``nsplit`` > 1 cuts every item's keys into that
+    many shares (decode rows over long contexts); ``scratch`` then holds ``attn_flex_scratch_floats`` floats."""
+    _cuda(q, k_cache, v_cache, block_table, items, out, dist_bias, sink, scratch, status)
+    _i32(block_table, "block_table"); _i32(items, "items")
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+          and (v_cache is None or v_cache.dtype == torch.bfloat16), "attn_flex: bfloat16 tensors only")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == H * dk and out.shape[1] == H * dv,
+          "attn_flex: q must be [T, H*dk], out [T, H*dv]")
+    _need(tuple(k_cache.shape[1:]) == (KV, page_size, dk) and k_cache.is_contiguous(), "attn_flex: keys must be [pages, KV, page_size, dk]")
+    if v_cache is not None:
+        _need(tuple(v_cache.shape) == (k_cache.shape[0], KV, page_size, dv) and v_cache.is_contiguous(),
+              "attn_flex: values must be [pages, KV, page_size, dv]")
+    _need(items.dim() == 2 and items.shape[1] == 4, "attn_flex: items must be int32 [n, 4]")
+    _need(q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and k_cache.data_ptr() % 16 == 0
+          and (v_cache is None or v_cache.data_ptr() % 16 == 0) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0,
+          "attn_flex: q and the caches must be 16-byte aligned")
+    nd = 0
+    if dist_bias is not None:
+        _need(dist_bias.dim() == 2 and dist_bias.shape[1] == H, "attn_flex: dist_bias must be [nd, H]")
+        _f32v(dist_bias, "dist_bias")
+        nd = dist_bias.shape[0]
+    _f32v(sink, "sink", H)
+    if nsplit > 1:
+        need = attn_flex_scratch_floats(items.shape[0], H, KV, dv, nsplit)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need,
+              f"attn_flex: scratch must hold {need} floats")
+    f = _fn("attention_flex", "si_attn_flex",
+            [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(items),
+             items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs, H, KV, dk, dv,
+             float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), _ptr(status),
+             _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)

@@ -28,6 +28,9 @@ KINDS = {
     "attn_decode_tma": "attn_decode_tma", "attn_portion_tc05": "attn_portion_tc05", "gemm_skinny": "gemm_skinny",
     "gemm_skinny_swiglu": "gemm_skinny_swiglu", "gemm_skinny_qkv_rope": "gemm_skinny_qkv_rope", "gemm_tc05": "gemm_tc05", "gemm_tc05_swiglu": "gemm_tc05_swiglu",
     "gemm_rows": "gemm_rows", "gemm_rows_swiglu": "gemm_rows_swiglu",
+    "embedding_pair": "embedding", "rmsnorm_rows": "rmsnorm_rows", "attention_general": "attention_general",
+    "attn_flex": "attn_flex", "kv_store": "kv_store", "latent_prepare": "latent_prepare", "activation": "activation",
+    "causal_conv": "causal_conv", "ssm_scan": "ssm_scan", "gated_part_norm": "gated_part_norm",
 }
 
 

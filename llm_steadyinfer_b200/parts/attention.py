@@ -28,6 +28,7 @@ import torch
 
 from ..csrc import ops
 from .base import CacheNeed, Mixer, register_mixer
+from . import flex_plan
 from . import linear as linear_mod
 from .linear import linear
 
@@ -109,7 +110,8 @@ class Attention(Mixer):
 
     def kernel_files(self, page_size):
         if self.general:
-            return ("attention_general",) + (("gemm_f32",) if self.dtype == torch.float32 else ("gemm_skinny", "gemm_rows", "gemm_tc05"))
+            return ("attention_general",) + (("gemm_f32",) if self.dtype == torch.float32
+                                             else ("attention_flex", "gemm_skinny", "gemm_rows", "gemm_tc05"))
         names = ["rope_kv"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_skinny", "gemm_rows", "gemm_tc05"])
         if not self.uses_tensor_cores():
             return tuple(names + ["attention_ref"])
@@ -163,9 +165,14 @@ class Attention(Mixer):
             ops.kv_store(qkv, ctx.positions, ctx.row_seq, cache.block_table, cache.k, cache.v, cache.page_size,
                          ctx.seq_slots, H, KV, hs, vs, status=ctx.status)
         attn = ctx.buf("attn_out", (T, H * vs), self.dtype)
-        ops.attention_general(qkv[:, :H * hs], cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions, attn,
-                              cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale, self.window or 0,
-                              dist_bias=self.dist_bias, status=ctx.status)
+        if self.uses_flex():
+            flex_plan.attend(flex_plan.plan(ctx, self.device, H, KV, hs, vs, True, self.window), qkv[:, :H * hs], cache.k,
+                             cache.v, cache.block_table, attn, cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale,
+                             self.window, dist_bias=self.dist_bias, status=ctx.status)
+        else:
+            ops.attention_general(qkv[:, :H * hs], cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions, attn,
+                                  cache.page_size, ctx.seq_slots, H, KV, hs, vs, self.scale, self.window or 0,
+                                  dist_bias=self.dist_bias, status=ctx.status)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(attn, self.o, out, ctx.status)
         return out
@@ -175,6 +182,11 @@ class Attention(Mixer):
         """Decode attention blocks that run at once on this part's device."""
         return DECODE_BLOCKS_PER_SM * ops.sm_count(self.device)
 
+    def uses_flex(self) -> bool:
+        """The general form on the tensor cores: bfloat16 and sizes in multiples of 8."""
+        return (self.general and self.dtype == torch.bfloat16 and USE_TENSOR_CORES
+                and ops.attn_flex_ok(self.H, self.KV, self.hs, self.vs, True))
+
     def uses_tensor_cores(self) -> bool:
         return not self.general and self.dtype == torch.bfloat16 and USE_TENSOR_CORES and self.hs % 16 == 0
 
@@ -182,7 +194,11 @@ class Attention(Mixer):
         """Cut the step's sequences into work items for the tensor-core kernels: runs of few
         tokens (decode rows) for the decode kernel, longer portions in runs of the portion
         kernel's item size. One plan serves every layer with the same head layout and window."""
-        if self.general or not self.uses_tensor_cores():
+        if self.general:
+            if self.uses_flex() and cache.k is not None:
+                flex_plan.plan(ctx, self.device, self.H, self.KV, self.hs, self.vs, True, self.window)
+            return
+        if not self.uses_tensor_cores():
             return
         key = ("attention", self.H, self.KV, self.hs, self.window)
         if key in ctx.plans or cache.k is None:

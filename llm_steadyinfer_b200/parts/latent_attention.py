@@ -21,9 +21,13 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from . import flex_plan
 from .base import CacheNeed, Mixer, register_mixer
 from .linear import linear
 from .rotary import rotary_inverse_frequencies
+
+
+USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
 
 
 class LatentAttention(Mixer):
@@ -90,7 +94,15 @@ class LatentAttention(Mixer):
 
     def kernel_files(self, page_size):
         names = ("attention_general", "norm")
-        return names + (("gemm_f32",) if self.dtype == torch.float32 else ("gemm_skinny", "gemm_rows", "gemm_tc05"))
+        return names + (("gemm_f32",) if self.dtype == torch.float32 else ("attention_flex", "gemm_skinny", "gemm_rows", "gemm_tc05"))
+
+    def uses_flex(self) -> bool:
+        """Attention on the tensor cores: bfloat16 and sizes in multiples of 8."""
+        return USE_TENSOR_CORES and self.dtype == torch.bfloat16 and ops.attn_flex_ok(self.H, 1, self.rk + self.dr, self.rk, False)
+
+    def prepare(self, ctx, cache):
+        if self.uses_flex() and cache.k is not None:
+            flex_plan.plan(ctx, self.device, self.H, 1, self.rk + self.dr, self.rk, False, self.window)
 
     def forward(self, x, ctx, cache):
         T = x.shape[0]
@@ -109,9 +121,14 @@ class LatentAttention(Mixer):
                            ctx.positions, ctx.row_seq, cache.block_table, cache.k if cache.writes else None,
                            cache.page_size, ctx.seq_slots, H, dq, dr, rk, status=ctx.status)
         o_lat = ctx.buf("lat_olat", (T, H * rk), self.dtype)
-        ops.attention_general(q_full, cache.k, None, cache.block_table, ctx.row_seq, ctx.positions, o_lat, cache.page_size,
-                              ctx.seq_slots, H, 1, rk + dr, rk, self.scale, self.window or 0, sink=self.sink,
-                              status=ctx.status)
+        if self.uses_flex():
+            flex_plan.attend(flex_plan.plan(ctx, self.device, H, 1, rk + dr, rk, False, self.window), q_full, cache.k, None,
+                             cache.block_table, o_lat, cache.page_size, ctx.seq_slots, H, 1, rk + dr, rk, self.scale,
+                             self.window, sink=self.sink, status=ctx.status)
+        else:
+            ops.attention_general(q_full, cache.k, None, cache.block_table, ctx.row_seq, ctx.positions, o_lat, cache.page_size,
+                                  ctx.seq_slots, H, 1, rk + dr, rk, self.scale, self.window or 0, sink=self.sink,
+                                  status=ctx.status)
         attn = ctx.buf("attn_out", (T, H * dv), self.dtype)
         for i in range(H):
             linear(o_lat[:, i * rk:(i + 1) * rk], self.uv[i], attn[:, i * dv:(i + 1) * dv], ctx.status)

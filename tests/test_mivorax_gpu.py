@@ -164,14 +164,9 @@ def _paged(keys, page_size, perm_seed):
     return cache, pages.to(torch.int32).view(1, -1)
 
 
-@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("case", ["bias", "sink_latent"])
-def test_attention_kernel_far_keys_and_edges(case, dtype):
-    """The general attention kernel on built inputs: one key far back (and keys at page borders, and at both sides of
-    every bucket edge of the bias) carries nearly all the weight of some query; its value row is unlike all others."""
-    from llm_steadyinfer_b200.csrc import ops
-    from llm_steadyinfer_b200.parts.attention import spread_by_distance
-    dev = "cuda:0"
+def _built_attention(case, dtype):
+    """Queries, keys and values in which one key far back (and keys at page borders, and at both sides of every bucket
+    edge of the bias) carries nearly all the weight of some query; plain result in float64."""
     torch.manual_seed(1)
     n, H, KV, dk, ps = 700, 4, 2, 32, 16
     dv = 48 if case == "bias" else 24
@@ -183,9 +178,8 @@ def test_attention_kernel_far_keys_and_edges(case, dtype):
     rows, dmax = 12, 300.0
     rel = torch.randn(rows, H) * 3.0
     edges = sorted({0, 1, rows // 2 - 1, rows // 2} | {d for d in range(1, 340) if pm.distance_bucket(d, rows, dmax) != pm.distance_bucket(d - 1, rows, dmax)}
-                   | {299, 300, 301, 15, 16, 17, 640})
-    # query i = 650 + e looks hard at the key `edges[e]` back
-    for e, dist in enumerate(edges):
+                   | {299, 300, 301, 15, 16, 17, 63, 64, 65, 640})
+    for e, dist in enumerate(edges):                      # query i = 650 + e looks hard at the key `dist` back
         i = 650 + e
         if i >= n or i - dist < 0:
             continue
@@ -196,7 +190,6 @@ def test_attention_kernel_far_keys_and_edges(case, dtype):
     q, k, v = (t.to(dtype).float() for t in (q, k, v))
     sink = torch.tensor([-2.0, 0.5, 3.0, 40.0])
     scale = 0.7
-    # plain: per head softmax over j <= i
     ref = torch.zeros(n, H, dv, dtype=torch.float64)
     by_distance = torch.tensor([pm.distance_bucket(d, rows, dmax) for d in range(n)])
     idx = by_distance[(torch.arange(n)[:, None] - torch.arange(n)[None, :]).clamp(min=0)]
@@ -206,18 +199,77 @@ def test_attention_kernel_far_keys_and_edges(case, dtype):
         bias = rel[:, h].double()[idx] if case == "bias" else None
         ref[:, h] = pm.softmax_attention(q[:, h].double(), k[:, g].double(), vv.double(), scale, bias=bias,
                                          sink=None if case == "bias" else sink[h].double())
-    kc, table = _paged(k.to(dtype), ps, 3)
-    vc = _paged(v.to(dtype), ps, 3)[0] if case == "bias" else None
+    return dict(n=n, H=H, KV=KV, dk=dk, dv=dv, ps=ps, q=q, k=k, v=v, rel=rel, dmax=dmax, sink=sink, scale=scale, ref=ref)
+
+
+@pytest.mark.parametrize("kernel,dtype", [("general", torch.float32), ("general", torch.bfloat16), ("flex", torch.bfloat16)],
+                         ids=["general-fp32", "general-bf16", "flex-bf16"])
+@pytest.mark.parametrize("case", ["bias", "sink_latent"])
+def test_attention_kernels_far_keys_and_edges(case, kernel, dtype):
+    """The general attention kernels (plain and tensor-core) on built inputs; the tensor-core one as portions, and its
+    last rows once more as single rows with their keys cut into shares that a second kernel merges."""
+    from llm_steadyinfer_b200.csrc import ops
+    from llm_steadyinfer_b200.parts.attention import spread_by_distance
+    dev = "cuda:0"
+    b = _built_attention(case, dtype)
+    n, H, KV, dk, dv, ps = b["n"], b["H"], b["KV"], b["dk"], b["dv"], b["ps"]
+    kc, table = _paged(b["k"].to(dtype), ps, 3)
+    vc = _paged(b["v"].to(dtype), ps, 3)[0].to(dev) if case == "bias" else None
+    bias = spread_by_distance(b["rel"], b["dmax"]).to(dev) if case == "bias" else None
+    sink = b["sink"].to(dev) if case != "bias" else None
+    qd = b["q"].to(dtype).view(n, H * dk).to(dev)
+    limit = 1e-4 if dtype == torch.float32 else 3e-2
     out = torch.zeros(n, H * dv, dtype=dtype, device=dev)
-    ops.attention_general(q.to(dtype).view(n, H * dk).to(dev), kc.to(dev), None if vc is None else vc.to(dev), table.to(dev),
-                          torch.zeros(n, dtype=torch.int32, device=dev), torch.arange(n, dtype=torch.int32, device=dev), out,
-                          ps, 1, H, KV, dk, dv, scale, 0,
-                          dist_bias=spread_by_distance(rel, dmax).to(dev) if case == "bias" else None,
-                          sink=sink.to(dev) if case != "bias" else None)
-    diff = (out.double().cpu().view(n, H, dv) - ref).abs().max().item()
-    assert diff <= (1e-4 if dtype == torch.float32 else 3e-2), f"{case}: differs by {diff:.2e}"
-    if case != "bias":        # a sink far above every score leaves almost nothing
-        assert out.view(n, H, dv)[:600, 3].abs().max().item() < 1e-6         # (rows from 650 on hold the built queries)
+    if kernel == "general":
+        ops.attention_general(qd, kc.to(dev), vc, table.to(dev), torch.zeros(n, dtype=torch.int32, device=dev),
+                              torch.arange(n, dtype=torch.int32, device=dev), out, ps, 1, H, KV, dk, dv, b["scale"], 0,
+                              dist_bias=bias, sink=sink)
+    else:
+        per = ops.attn_flex_tokens(H, KV)
+        items = torch.tensor([(0, r, min(per, n - r), r) for r in range(0, n, per)], dtype=torch.int32, device=dev)
+        ops.attn_flex(qd, kc.to(dev), vc, table.to(dev), items, out, ps, 1, H, KV, dk, dv, b["scale"], 0, dist_bias=bias, sink=sink)
+        ones = torch.tensor([(0, r, 1, r) for r in range(600, n)], dtype=torch.int32, device=dev)
+        again = torch.zeros_like(out)
+        scratch = torch.zeros(ops.attn_flex_scratch_floats(ones.shape[0], H, KV, dv, 5), dtype=torch.float32, device=dev)
+        ops.attn_flex(qd, kc.to(dev), vc, table.to(dev), ones, again, ps, 1, H, KV, dk, dv, b["scale"], 0, dist_bias=bias, sink=sink,
+                      nsplit=5, scratch=scratch)
+        diff = (again[600:].double().cpu().view(-1, H, dv) - b["ref"][600:]).abs().max().item()
+        assert diff <= limit, f"{case}: rows in shares differ by {diff:.2e}"
+    diff = (out.double().cpu().view(n, H, dv) - b["ref"]).abs().max().item()
+    assert diff <= limit, f"{case}: differs by {diff:.2e}"
+    if case != "bias":        # a sink far above every score leaves almost nothing (rows from 650 on hold the built queries)
+        assert out.view(n, H, dv)[:600, 3].abs().max().item() < 1e-6
+
+
+@pytest.mark.parametrize("H,KV,dk,dv,own_v", [(8, 2, 64, 32, True), (4, 1, 48, 80, True), (16, 1, 160, 128, False),
+                                              (128, 1, 72, 64, False), (6, 3, 192, 160, True), (2, 1, 576, 512, False)])
+def test_tensor_core_attention_sizes(H, KV, dk, dv, own_v):
+    """The tensor-core kernel against the plain one at head layouts that take its different routes: value slices, key
+    tiles of 32, more heads than a tile has rows, sizes that are no multiple of 16."""
+    from llm_steadyinfer_b200.csrc import ops
+    dev = "cuda:0"
+    torch.manual_seed(H + dk)
+    n, ps = 150, 16
+    k = (torch.randn(n, KV, dk) * 0.5).bfloat16()
+    v = torch.randn(n, KV, dv).bfloat16() if own_v else None
+    q = (torch.randn(n, H * dk) * 0.5).bfloat16().to(dev)
+    kc, table = _paged(k, ps, 5)
+    vc = _paged(v, ps, 5)[0].to(dev) if own_v else None
+    sink = torch.randn(H, device=dev)
+    bias = torch.randn(40, H, device=dev)
+    want = torch.zeros(n, H * dv, dtype=torch.bfloat16, device=dev)
+    seqs, pos = torch.zeros(n, dtype=torch.int32, device=dev), torch.arange(n, dtype=torch.int32, device=dev)
+    ops.attention_general(q, kc.to(dev), vc, table.to(dev), seqs, pos, want, ps, 1, H, KV, dk, dv, dk ** -0.5, 0, dist_bias=bias, sink=sink)
+    per = ops.attn_flex_tokens(H, KV)
+    items = torch.tensor([(0, r, min(per, n - r), r) for r in range(0, n, per)], dtype=torch.int32, device=dev)
+    got = torch.zeros_like(want)
+    ops.attn_flex(q, kc.to(dev), vc, table.to(dev), items, got, ps, 1, H, KV, dk, dv, dk ** -0.5, 0, dist_bias=bias, sink=sink)
+    assert (got.float() - want.float()).abs().max().item() <= 2e-2
+    ones = torch.tensor([(0, r, 1, r) for r in range(n)], dtype=torch.int32, device=dev)
+    scratch = torch.zeros(ops.attn_flex_scratch_floats(n, H, KV, dv, 3), dtype=torch.float32, device=dev)
+    got.zero_()
+    ops.attn_flex(q, kc.to(dev), vc, table.to(dev), ones, got, ps, 1, H, KV, dk, dv, dk ** -0.5, 0, dist_bias=bias, sink=sink, nsplit=3, scratch=scratch)
+    assert (got.float() - want.float()).abs().max().item() <= 2e-2
 
 
 def test_bias_table_is_spread_as_the_plain_bucket_says():
@@ -236,7 +288,7 @@ def test_state_space_kernels_in_portions(heads, P, N, groups, taps):
     from llm_steadyinfer_b200.csrc import ops
     dev = "cuda:0"
     torch.manual_seed(heads * 100 + N)
-    T = 83
+    T = 84
     inner, C = heads * P, heads * P + 2 * groups * N
     u = torch.randn(T, C + heads + inner)                     # [z | xBC | dt] rows as the projection lays them out
     conv_w, conv_b = torch.randn(C, taps) * 0.5, torch.randn(C) * 0.1
