@@ -26,6 +26,7 @@ struct FlexParams {
   const float* dist_bias; int nd;                // fp32 [nd, H] or nullptr
   const float* sink;                             // fp32 [H] or nullptr
   int num_pages, page_size, num_seqs, H, KV, G, Gb, hparts, dk, dv, dk_pitch;
+  int bias_in_smem;         // the distances a key tile can meet are staged in shared memory, tile by tile
   float scale_log2;         // scale * log2(e)
   int window, nsplit;
   int* status;
@@ -50,6 +51,9 @@ attn_flex_kernel(const FlexParams p) {
   bf16* Ks = Qs + (size_t)FLEX_M * p.dk_pitch;          // [2][BLOCK_N][dk_pitch]
   bf16* Vs = Ks + (size_t)2 * BLOCK_N * p.dk_pitch;     // [2][BLOCK_N][DVB]  (own values only)
   const bool own_v = p.v_cache != nullptr;
+  // [2][BLOCK_N + 64 / Gb][Gb] biases of the distances that the rows of this block have to the keys of a tile
+  float* Bs = reinterpret_cast<float*>(Vs + (own_v ? (size_t)2 * BLOCK_N * DVB : 0));
+  const int bwin = BLOCK_N + FLEX_M / p.Gb;
 
   const int item_idx = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
   const AttnItem item = p.items[item_idx];
@@ -111,6 +115,14 @@ attn_flex_kernel(const FlexParams p) {
         cp_async16(ftile(Vt, DT, row, c), p.v_cache + off, valid);
       }
     }
+    if (p.bias_in_smem) {                     // entry (d - dlo, head) with dlo the least distance of the tile
+      float* Bt = Bs + (size_t)stage * bwin * p.Gb;
+      const int dlo = item.pos0 - (j0 + BLOCK_N - 1);
+      for (int id = threadIdx.x; id < bwin * p.Gb; id += THREADS) {
+        const int d = dlo + id / p.Gb;
+        Bt[id] = d < 0 ? 0.f : p.dist_bias[(size_t)min(d, p.nd - 1) * p.H + head0 + id % p.Gb] * LOG2E;
+      }
+    }
   };
 
   if (ntiles > 0) {
@@ -130,7 +142,8 @@ attn_flex_kernel(const FlexParams p) {
   const int tok_lo = r_lo / p.Gb, tok_hi = r_hi / p.Gb;
   const int pos_lo = tok_lo < item.ntok ? item.pos0 + tok_lo : -1;     // -1: row unused
   const int pos_hi = tok_hi < item.ntok ? item.pos0 + tok_hi : -1;
-  const int head_lo = head0 + r_lo % p.Gb, head_hi = head0 + r_hi % p.Gb;
+  const int hh_lo = r_lo % p.Gb, hh_hi = r_hi % p.Gb;
+  const int head_lo = head0 + hh_lo, head_hi = head0 + hh_hi;
   const int warp_last_tok = min(item.ntok - 1, (warp * 16 + 15) / p.Gb);
   const int warp_first_tok = (warp * 16) / p.Gb;
   const bool warp_active = warp_first_tok < item.ntok;
@@ -172,6 +185,8 @@ attn_flex_kernel(const FlexParams p) {
         }
       }
       float mx_lo = m_lo, mx_hi = m_hi;
+      const float* Bt = Bs + (size_t)(t & 1) * bwin * p.Gb;
+      const int dlo = item.pos0 - (j0 + BLOCK_N - 1);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -182,7 +197,8 @@ attn_flex_kernel(const FlexParams p) {
           float v = -INFINITY;
           if (vis) {
             v = s[nt][e] * p.scale_log2;
-            if (p.dist_bias) v += p.dist_bias[(size_t)min(pos - j, p.nd - 1) * p.H + ((e < 2) ? head_lo : head_hi)] * LOG2E;
+            if (p.bias_in_smem) v += Bt[(pos - j - dlo) * p.Gb + ((e < 2) ? hh_lo : hh_hi)];
+            else if (p.dist_bias) v += p.dist_bias[(size_t)min(pos - j, p.nd - 1) * p.H + ((e < 2) ? head_lo : head_hi)] * LOG2E;
           }
           s[nt][e] = v;
           if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -278,29 +294,39 @@ attn_flex_kernel(const FlexParams p) {
   }
 }
 
-// Merge of the shares of split items: one block per (item, gy), a thread per (row, value column).
+// Merge of the shares of split items: one block per (item, gy, row); the first threads weigh the shares, then a
+// thread per value column adds them up.
 __global__ void attn_flex_merge_kernel(const FlexParams p) {
+  __shared__ float w[64];
+  __shared__ float s_inv;
   pdl_prologue();
   const AttnItem item = p.items[blockIdx.x];
   if (item.ntok <= 0 || item.seq < 0 || item.seq >= p.num_seqs) return;
+  const int r = blockIdx.z;
+  if (r >= item.ntok * p.Gb) return;
   const int g = blockIdx.y / p.hparts, hpart = blockIdx.y % p.hparts;
-  const int head0 = g * p.G + hpart * p.Gb;
+  const int tok = r / p.Gb, head = g * p.G + hpart * p.Gb + r % p.Gb;
   const size_t slab0 = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit;
-  const int rows = item.ntok * p.Gb;
-  for (int idx = threadIdx.x; idx < rows * p.dv; idx += blockDim.x) {
-    const int r = idx / p.dv, d = idx % p.dv;
-    const int tok = r / p.Gb, hh = r - tok * p.Gb;
-    float M = p.sink ? p.sink[head0 + hh] * LOG2E : -INFINITY;
-    for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, p.part_ml[((slab0 + s) * FLEX_M + r) * 2]);
-    float L = p.sink ? exp2f(p.sink[head0 + hh] * LOG2E - M) : 0.f, acc = 0.f;
-    for (int s = 0; s < p.nsplit; ++s) {
-      const float m = p.part_ml[((slab0 + s) * FLEX_M + r) * 2];
-      if (m == -INFINITY) continue;                         // a share without keys
-      const float w = exp2f(m - M);
-      L += p.part_ml[((slab0 + s) * FLEX_M + r) * 2 + 1] * w;
-      acc += p.part_o[((slab0 + s) * FLEX_M + r) * p.dv + d] * w;
-    }
-    p.out[(size_t)(item.row0 + tok) * p.out_stride + (size_t)(head0 + hh) * p.dv + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  if (threadIdx.x < 32) {                                 // nsplit <= 64: two shares a lane
+    const int s0 = threadIdx.x, s1 = threadIdx.x + 32;
+    const float m0 = s0 < p.nsplit ? p.part_ml[((slab0 + s0) * FLEX_M + r) * 2] : -INFINITY;
+    const float m1 = s1 < p.nsplit ? p.part_ml[((slab0 + s1) * FLEX_M + r) * 2] : -INFINITY;
+    const float sk = p.sink ? p.sink[head] * LOG2E : -INFINITY;
+    const float M = fmaxf(warp_max(fmaxf(m0, m1)), sk);
+    const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
+    float L = (s0 < p.nsplit ? p.part_ml[((slab0 + s0) * FLEX_M + r) * 2 + 1] * w0 : 0.f)
+            + (s1 < p.nsplit ? p.part_ml[((slab0 + s1) * FLEX_M + r) * 2 + 1] * w1 : 0.f);
+    L = warp_sum(L) + (p.sink ? exp2f(sk - M) : 0.f);
+    w[s0] = w0; w[s1] = w1;
+    if (threadIdx.x == 0) s_inv = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)head * p.dv;
+  for (int d = threadIdx.x; d < p.dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < p.nsplit; ++s)
+      if (w[s] > 0.f) acc += p.part_o[((slab0 + s) * FLEX_M + r) * p.dv + d] * w[s];
+    dst[d] = __float2bfloat16_rn(acc * s_inv);
   }
 }
 
@@ -341,7 +367,7 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
                            int dv, float scale, int window, const float* dist_bias, int nd, const float* sink,
                            int nsplit, float* scratch, int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
-  if (!si_attn_flex_ok(H, KV, dk, dv, v_cache != nullptr) || nsplit < 1 || (nsplit > 1 && !scratch)) return -2;
+  if (!si_attn_flex_ok(H, KV, dk, dv, v_cache != nullptr) || nsplit < 1 || nsplit > 64 || (nsplit > 1 && !scratch)) return -2;
   FlexParams p;
   p.q = (const bf16*)q; p.q_stride = q_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
@@ -360,15 +386,17 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
   const int block_n = p.dk_pitch > 256 ? 32 : 64;        // the two key stages and the queries share 227 KB
   const int dvb = dv > 64 ? 128 : 64;
   const int dslices = (dv + dvb - 1) / dvb;
-  const size_t smem = ((size_t)(FLEX_M + 2 * block_n) * p.dk_pitch + (own_v ? (size_t)2 * block_n * dvb : 0)) * sizeof(bf16);
+  size_t smem = ((size_t)(FLEX_M + 2 * block_n) * p.dk_pitch + (own_v ? (size_t)2 * block_n * dvb : 0)) * sizeof(bf16);
   if (smem > 227 * 1024) return -2;
+  const size_t bias_bytes = (size_t)2 * (block_n + FLEX_M / p.Gb) * p.Gb * sizeof(float);
+  p.bias_in_smem = dist_bias && smem + bias_bytes <= 227 * 1024 ? 1 : 0;       // else each score fetches its own
+  if (p.bias_in_smem) smem += bias_bytes;
   int rc;
   if (block_n == 64) rc = dvb == 128 ? flex_launch<64, 128>(p, dslices, smem, stream) : flex_launch<64, 64>(p, dslices, smem, stream);
   else rc = dvb == 128 ? flex_launch<32, 128>(p, dslices, smem, stream) : flex_launch<32, 64>(p, dslices, smem, stream);
   if (rc) return rc;
   if (nsplit > 1) {
-    const int threads = 256;
-    attn_flex_merge_kernel<<<dim3(num_items, KV * p.hparts), threads, 0, stream>>>(p);
+    attn_flex_merge_kernel<<<dim3(num_items, KV * p.hparts, FLEX_M), 128, 0, stream>>>(p);
   }
   return si_last_error();
 }

@@ -945,10 +945,34 @@ def causal_conv(u, weight, bias, state, conv_off: int, out, positions, row_seq, 
              _ptr(status), _stream()), f"causal_conv(channels={C}, taps={K})", kernels=2 if K > 1 else 1)
 
 
+def ssm_padded_state(N: int, P: int) -> int:
+    """State rows per head as the scan kernel keeps them: N rounded up to (lanes per column) x (entries per lane). The
+    same rule as ``scan_shape`` in ssm.cu, restated here so that a model's state size is known without the library;
+    ``ssm_padded_state_of_library`` asks the library, and a test holds the two together."""
+    ns = 32
+    while ns > 1 and (P * ns > 1024 or ns * 2 > N):
+        ns //= 2
+    while ns > 1 and P * ns > 512 and -(-N // (ns // 2)) <= 16:
+        ns //= 2
+    while ns > 1 and -(-N // ns) < 4:
+        ns //= 2
+    per = -(-N // ns)
+    if per > 32:
+        raise KernelError(f"ssm_scan: a state of {N} x {P} is outside what the kernel supports")
+    return ns * (4 if per <= 4 else 8 if per <= 8 else 16 if per <= 16 else 32)
+
+
+def ssm_padded_state_of_library(N: int, P: int) -> int:
+    lib = build.load("ssm")
+    lib.si_ssm_padded_state.restype = _c_int
+    return lib.si_ssm_padded_state(_c_int(N), _c_int(P))
+
+
 def ssm_scan(xbc, dt_raw, dt_bias, a_log, d_skip, state, y, q_start, ctx_len, slots, num_seqs: int, heads: int,
              groups: int, N: int, P: int) -> None:
-    """The recurrence over every sequence's rows of this step, from and into ``state[slot, :heads*N*P]`` (fp32, from
-    zero for a portion that starts at position 0). ``xbc`` fp32 [T, heads*P + 2*groups*N] = [x | B | C];
+    """The recurrence over every sequence's rows of this step, from and into the first
+    ``heads * ssm_padded_state(N, P) * P`` floats of ``state[slot]`` (fp32, in the kernel's own order; from zero for a
+    portion that starts at position 0). ``xbc`` fp32 [T, heads*P + 2*groups*N] = [x | B | C];
     ``dt_raw`` [T, heads] (compute dtype, a strided view); ``y`` fp32 [T, heads*P]."""
     _cuda(xbc, dt_raw, dt_bias, a_log, d_skip, state, y, q_start, ctx_len, slots)
     for t, nm in ((q_start, "q_start"), (ctx_len, "ctx_len"), (slots, "slots")):
@@ -958,8 +982,9 @@ def ssm_scan(xbc, dt_raw, dt_bias, a_log, d_skip, state, y, q_start, ctx_len, sl
           "ssm_scan: xbc must be fp32 [T, heads*P + 2*groups*N]")
     _need(dt_raw.shape == (T, heads) and dt_raw.stride(1) == 1, "ssm_scan: dt_raw must be [T, heads]")
     _need(y.dtype == torch.float32 and y.shape == (T, heads * P) and y.stride(1) == 1, "ssm_scan: y must be fp32 [T, heads*P]")
-    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= heads * N * P,
-          "ssm_scan: state must be fp32 [slots, >= heads*N*P]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state.shape[1] >= heads * ssm_padded_state(N, P) * P,
+          "ssm_scan: state must be fp32 [slots, >= heads * ssm_padded_state(N, P) * P]")
     _f32v(dt_bias, "dt_bias", heads); _f32v(a_log, "a_log", heads); _f32v(d_skip, "d_skip", heads)
     f = _fn("ssm", "si_ssm_scan",
             [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int,
@@ -1040,3 +1065,26 @@ def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_
              items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs, H, KV, dk, dv,
              float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), _ptr(status),
              _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
+
+
+# ---- one small matrix per head (decode rows) -----------------------------------------------------------------
+
+def gemm_heads_ok(a, w, out, H: int, a_head: int, o_head: int) -> bool:
+    """True when ``gemm_heads`` takes these tensors: bf16, at most 16 rows, K a multiple of 8, 16-byte aligned heads."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and a.shape[0] <= 16
+            and w.dim() == 3 and w.shape[0] == H and w.is_contiguous() and w.shape[2] % 8 == 0 and a.stride(1) == 1
+            and out.stride(1) == 1 and a.stride(0) % 8 == 0 and a_head % 8 == 0 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and a.shape[0] * w.shape[2] * 2 <= 48 * 1024)
+
+
+def gemm_heads(a, w, out, a_head: int, o_head: int) -> None:
+    """out[t, h*o_head : h*o_head + N] = a[t, h*a_head : h*a_head + K] @ w[h]^T for every head h of w [H, N, K], at
+    most 16 rows, in one launch (``a_head``, ``o_head``: distance between heads within a row, in elements)."""
+    _cuda(a, w, out)
+    H, N, K = w.shape
+    M = a.shape[0]
+    _need(gemm_heads_ok(a, w, out, H, a_head, o_head), "gemm_heads: bf16, at most 16 rows, K a multiple of 8, aligned heads")
+    _need(out.shape[0] == M and a.shape[1] >= (H - 1) * a_head + K and out.shape[1] >= (H - 1) * o_head + N, "gemm_heads: shapes")
+    f = _fn("gemm_heads", "si_gemm_heads", [_c_p, _c_ll, _c_ll, _c_p, _c_p, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), a.stride(0), int(a_head), _ptr(w), _ptr(out), out.stride(0), int(o_head), M, H, N, K, _stream()),
+           f"gemm_heads(M={M}, heads={H}, N={N}, K={K})")

@@ -3,7 +3,9 @@
 // and the sums; the inputs are the projection's output in the compute dtype.
 //
 // Per request the mixer keeps one fp32 vector in its state slot:
-//   [ recurrent state: heads * N * P | the convolution's last K - 1 inputs: (K - 1) * C ]
+//   [ recurrent state: heads * Npad * P | the convolution's last K - 1 inputs: (K - 1) * C ]
+// (Npad: N rounded up to what the scan's threads hold, si_ssm_padded_state; within a head the entries lie in the
+// order of the scan's threads, so that a block reads and writes its state in whole lines)
 // A portion of a sequence starts from what the slot holds (from zero when the portion starts at position 0) and
 // leaves behind what the next portion needs, so a sequence may be cut anywhere.
 //
@@ -114,9 +116,11 @@ SI_EXPORT int si_causal_conv(const void* u, int dtype, long long u_stride, const
 }
 
 // ---- the recurrence -------------------------------------------------------------------------------------------
-// One block per (sequence of the step, head). Thread (p, ns) keeps NPT entries S[ns * NPT + i, p] of the state in
-// registers; the NS threads of one p are neighbouring lanes and add their parts of y_t with shuffles. Tokens are
-// walked in order, SCAN_CHUNK at a time staged in shared memory (B, C, x, step size, decay).
+// One block per (sequence of the step, head). Thread (p, ns) keeps NPT entries of column p of the state in
+// registers, in groups of four neighbouring n: entry i is S[((i / 4) * NS + ns) * 4 + i % 4, p], so that the NS
+// threads of one p (neighbouring lanes) read B and C from shared memory as consecutive 16-byte words, without bank
+// conflicts; they add their parts of y_t with shuffles. Tokens are walked in order, SCAN_CHUNK at a time staged in
+// shared memory (B, C, x, step size, decay).
 #define SCAN_CHUNK 16
 
 template <typename T, int NPT>
@@ -127,7 +131,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
                                 float* __restrict__ y, long long y_stride, const int* __restrict__ q_start,
                                 const int* __restrict__ ctx_len, const int* __restrict__ slots, int heads,
                                 int groups, int N, int P, int NS) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_prologue();
   const int s = blockIdx.x, h = blockIdx.y;
   const int row0 = q_start[s], n_rows = q_start[s + 1] - row0;
@@ -145,13 +149,12 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
   const int ns = tid % NS;
   const bool live = tid / NS < P;          // the last warp may hold threads beyond the state's columns: they follow idly
   const int p = live ? tid / NS : 0;
-  float* st = state + (size_t)slots[s] * state_stride + (size_t)h * N * P;
+  // the head's state in the order of the threads: entry i of thread tid at i * (P * NS) + tid
+  float* st = state + (size_t)slots[s] * state_stride + (size_t)h * Npad * P;
+  const int held = P * NS;
   float S[NPT];
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) {
-    const int n = ns * NPT + i;
-    S[i] = (live && n < N && pos0 > 0) ? st[(size_t)n * P + p] : 0.f;
-  }
+  for (int i = 0; i < NPT; ++i) S[i] = (live && pos0 > 0) ? st[(size_t)i * held + tid] : 0.f;
   const float rate = expf(a_log[h]);
   const float bias = dt_bias[h];
   const float dskip = Dskip[h];
@@ -181,13 +184,16 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
       for (int r = 0; r < cn; ++r) {
         const float dec = sDec[r];
         const float dx = sX[r * P + p];
-        const float* Br = sB + r * Npad + ns * NPT;
-        const float* Cr = sC + r * Npad + ns * NPT;
+        const float4* Br = reinterpret_cast<const float4*>(sB + r * Npad) + ns;
+        const float4* Cr = reinterpret_cast<const float4*>(sC + r * Npad) + ns;
         float acc = 0.f;
 #pragma unroll
-        for (int i = 0; i < NPT; ++i) {
-          S[i] = fmaf(dec, S[i], dx * Br[i]);
-          acc = fmaf(S[i], Cr[i], acc);
+        for (int i4 = 0; i4 < NPT / 4; ++i4) {
+          const float4 b = Br[i4 * NS], c = Cr[i4 * NS];
+          S[4 * i4 + 0] = fmaf(dec, S[4 * i4 + 0], dx * b.x); acc = fmaf(S[4 * i4 + 0], c.x, acc);
+          S[4 * i4 + 1] = fmaf(dec, S[4 * i4 + 1], dx * b.y); acc = fmaf(S[4 * i4 + 1], c.y, acc);
+          S[4 * i4 + 2] = fmaf(dec, S[4 * i4 + 2], dx * b.z); acc = fmaf(S[4 * i4 + 2], c.z, acc);
+          S[4 * i4 + 3] = fmaf(dec, S[4 * i4 + 3], dx * b.w); acc = fmaf(S[4 * i4 + 3], c.w, acc);
         }
         for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, NS);
         if (ns == 0 && live) y[(size_t)(row0 + c0 + r) * y_stride + (size_t)h * P + p] = acc + dskip * sXr[r * P + p];
@@ -196,10 +202,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const int n = ns * NPT + i;
-      if (n < N) st[(size_t)n * P + p] = S[i];
-    }
+    for (int i = 0; i < NPT; ++i) st[(size_t)i * held + tid] = S[i];
   }
 }
 
@@ -220,6 +223,25 @@ static int scan_launch(const float* xbc, long long xbc_stride, const void* dt_ra
   return si_last_error();
 }
 
+// How the scan spreads a head's N x P state over its threads: NS lanes per column (a power of two up to 32), each
+// with NPT entries (4, 8, 16 or 32). Returns NS and sets *npt; N is padded to NS * NPT.
+static int scan_shape(int N, int P, int* npt) {
+  int NS = 32;
+  while (NS > 1 && (P * NS > 1024 || NS * 2 > N)) NS >>= 1;
+  while (NS > 1 && P * NS > 512 && (N + NS / 2 - 1) / (NS / 2) <= 16) NS >>= 1;     // fewer, fuller threads
+  while (NS > 1 && (N + NS - 1) / NS < 4) NS >>= 1;                                  // at least four entries each
+  const int per = (N + NS - 1) / NS;
+  *npt = per <= 4 ? 4 : per <= 8 ? 8 : per <= 16 ? 16 : 32;
+  return per > 32 ? 0 : NS;
+}
+
+// N rounded up to the state rows the scan keeps per head (the state tensor holds heads * this * P floats).
+SI_EXPORT int si_ssm_padded_state(int N, int P) {
+  int npt = 0;
+  const int NS = scan_shape(N, P, &npt);
+  return NS * npt;
+}
+
 SI_EXPORT int si_ssm_scan(const float* xbc, long long xbc_stride, const void* dt_raw, int dtype, long long dt_stride,
                           const float* dt_bias, const float* a_log, const float* Dskip, float* state,
                           long long state_stride, float* y, long long y_stride, const int* q_start,
@@ -227,13 +249,9 @@ SI_EXPORT int si_ssm_scan(const float* xbc, long long xbc_stride, const void* dt
                           cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || P > 1024 || heads > 65535) return -2;
-  // lanes per column of the state: a power of two up to 32, as many as keep the block within 1024 threads and give
-  // every thread at most 32 state entries
-  int NS = 32;
-  while (NS > 1 && (P * NS > 1024 || NS * 2 > N)) NS >>= 1;
-  while (NS > 1 && P * NS > 512 && (N + NS / 2 - 1) / (NS / 2) <= 16) NS >>= 1;     // fewer, fuller threads
-  const int per = (N + NS - 1) / NS;
-  if (per > 32) return -2;
+  int per = 0;
+  const int NS = scan_shape(N, P, &per);
+  if (NS == 0) return -2;
 #define SCAN_GO(TT, NPT) scan_launch<TT, NPT>(xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, Dskip, state, \
                                               state_stride, y, y_stride, q_start, ctx_len, slots, num_seqs, heads, \
                                               groups, N, P, NS, stream)

@@ -94,7 +94,7 @@ class LatentAttention(Mixer):
 
     def kernel_files(self, page_size):
         names = ("attention_general", "norm")
-        return names + (("gemm_f32",) if self.dtype == torch.float32 else ("attention_flex", "gemm_skinny", "gemm_rows", "gemm_tc05"))
+        return names + (("gemm_f32",) if self.dtype == torch.float32 else ("attention_flex", "gemm_heads", "gemm_skinny", "gemm_rows", "gemm_tc05"))
 
     def uses_flex(self) -> bool:
         """Attention on the tensor cores: bfloat16 and sizes in multiples of 8."""
@@ -115,8 +115,11 @@ class LatentAttention(Mixer):
         linear(cq, self.uq, q, ctx.status)
         # queries against the cached latents: [W_uk,i^T q_plain,i | rotated part] per head
         q_full = ctx.buf("lat_qfull", (T, H * (rk + dr)), self.dtype)
-        for i in range(H):
-            linear(q[:, i * (dq + dr): i * (dq + dr) + dq], self.ukT[i], q_full[:, i * (rk + dr): i * (rk + dr) + rk], ctx.status)
+        if ops.gemm_heads_ok(q, self.ukT, q_full, H, dq + dr, rk + dr):          # few rows: all heads in one launch
+            ops.gemm_heads(q, self.ukT, q_full, dq + dr, rk + dr)
+        else:
+            for i in range(H):
+                linear(q[:, i * (dq + dr): i * (dq + dr) + dq], self.ukT[i], q_full[:, i * (rk + dr): i * (rk + dr) + rk], ctx.status)
         ops.latent_prepare(lat[:, self.q_rank:], q, q_full, self.kv_norm, self.eps, self.inv_freq, self.rot_dims,
                            ctx.positions, ctx.row_seq, cache.block_table, cache.k if cache.writes else None,
                            cache.page_size, ctx.seq_slots, H, dq, dr, rk, status=ctx.status)
@@ -130,8 +133,11 @@ class LatentAttention(Mixer):
                                   ctx.seq_slots, H, 1, rk + dr, rk, self.scale, self.window or 0, sink=self.sink,
                                   status=ctx.status)
         attn = ctx.buf("attn_out", (T, H * dv), self.dtype)
-        for i in range(H):
-            linear(o_lat[:, i * rk:(i + 1) * rk], self.uv[i], attn[:, i * dv:(i + 1) * dv], ctx.status)
+        if ops.gemm_heads_ok(o_lat, self.uv, attn, H, rk, dv):
+            ops.gemm_heads(o_lat, self.uv, attn, rk, dv)
+        else:
+            for i in range(H):
+                linear(o_lat[:, i * rk:(i + 1) * rk], self.uv[i], attn[:, i * dv:(i + 1) * dv], ctx.status)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(attn, self.o, out, ctx.status)
         return out

@@ -10,7 +10,8 @@ Per row h_t, with ``heads`` heads of size P, state size N, ``groups`` groups of 
     g = y * silu(z);   out = W_o (norm_parts(g) * w)          RMS norm over ``norm_groups`` equal parts of the row
 Head h reads the B and C of group ``h // (heads / groups)``.
 
-A request's state is one fp32 vector per slot, ``[S: heads*N*P | last taps-1 conv inputs: (taps-1) * channels]``;
+A request's state is one fp32 vector per slot, ``[S: heads*Npad*P | last taps-1 conv inputs: (taps-1) * channels]``
+(Npad: N rounded up to what the scan kernel's threads hold);
 the kernels start a portion from it and leave the next portion's behind (``csrc/ssm.cu``), so prompts can be cut
 anywhere and decoding is the same path with one row. Step size, decay, state, the gate and the norm are fp32 in both
 precisions.
@@ -48,7 +49,7 @@ class StateSpace(Mixer):
             raise ValueError(f"state_space: inner size {self.inner} does not split into {self.norm_groups} norm groups")
         if not 1 <= self.taps <= 17:
             raise ValueError(f"state_space: {self.taps} convolution taps are not supported (1 to 17)")
-        self.conv_off = self.heads * self.N * self.P
+        self.conv_off = self.heads * ops.ssm_padded_state(self.N, self.P) * self.P      # the scan's part of the slot
         self.w_in = self.w_o = None
         self.conv_w = self.conv_b = self.dt_bias = self.a_log = self.d_skip = self.norm_w = None
 

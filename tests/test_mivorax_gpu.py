@@ -299,7 +299,8 @@ def test_state_space_kernels_in_portions(heads, P, N, groups, taps):
     y = pm.state_space_scan(xbc[:, :inner].contiguous(), xbc[:, inner:inner + groups * N].contiguous(), xbc[:, inner + groups * N:].contiguous(),
                             pm.softplus(dt_raw.double() + dt_bias.double()), a_log.double(), dsk.double(), heads, groups)
     want = pm.rms_norm((y * pm.silu(z.double())).view(T, 2, inner // 2), None, 1e-5).reshape(T, inner) * norm_w.double()
-    conv_off = heads * N * P
+    assert ops.ssm_padded_state(N, P) == ops.ssm_padded_state_of_library(N, P)
+    conv_off = heads * ops.ssm_padded_state(N, P) * P
     state = torch.randn(3, conv_off + (taps - 1) * C, device=dev)          # stale contents
     got = torch.zeros(T, inner, device=dev)
     ud = u.to(dev)
@@ -390,3 +391,20 @@ def test_trace_program(folders, plains, tmp_path):
                 assert row_error(rows[r], plains[name].of(reqs[e["id"]])[base + wpos]) <= LIMIT[torch.float32]
                 r += 1
             pos[e["id"]] = base + len(e["tokens"])
+
+
+@pytest.mark.parametrize("M,H,N,K,a_head,o_head", [(1, 3, 56, 24, 40, 72), (8, 16, 512, 128, 192, 576), (16, 5, 40, 56, 56, 40), (7, 4, 9, 640, 640, 16)])
+def test_per_head_product(M, H, N, K, a_head, o_head):
+    """One launch for all heads' small matrices against torch, heads lying inside wider rows."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(M + H)
+    a = torch.randn(M, (H - 1) * a_head + K + 8, device="cuda:0").bfloat16()
+    w = (torch.randn(H, N, K, device="cuda:0") / K ** 0.5).bfloat16()
+    out = torch.full((M, (H - 1) * o_head + N + 4), 7.0, device="cuda:0").bfloat16()
+    assert ops.gemm_heads_ok(a, w, out, H, a_head, o_head)
+    ops.gemm_heads(a, w, out, a_head, o_head)
+    for h in range(H):
+        want = a[:, h * a_head:h * a_head + K].float() @ w[h].float().T
+        assert (out[:, h * o_head:h * o_head + N].float() - want).abs().max().item() <= 2e-2
+    if o_head > N:
+        assert (out[:, N:o_head] == 7.0).all()            # nothing written between the heads

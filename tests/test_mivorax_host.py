@@ -60,7 +60,9 @@ def test_checkpoint_names_shapes_and_state(tmp_path):
     needs, states = model.cache_places()
     assert len(needs) == 8 and needs[-1] is None and states[-1].dtype == torch.int32
     assert needs[2].value_dim == 0 and needs[2].head_dim == 128 and needs[1].v_dim == 16
-    assert states[0].shape == (4 * 16 * 24 + 3 * (96 + 64),) and states[1] is None
+    assert states[0].shape == (4 * 16 * 24 + 3 * (96 + 64),) and states[1] is None      # a state of 16 rows needs no padding
+    from llm_steadyinfer_b200.csrc import ops
+    assert [ops.ssm_padded_state(n, p) for n, p in ((16, 24), (128, 64), (5, 8), (48, 48), (64, 32), (8, 32))] == [16, 128, 8, 64, 64, 8]
     # a table with other rows than the configuration says is refused
     bad = copy.deepcopy(mc.MIXED_A)
     bad["layers"][1]["mixer"]["bias_buckets"] = 20
