@@ -199,12 +199,13 @@ SI_EXPORT int si_kv_store(const void* qkv, int dtype, long long row_stride, cons
 //   kv = [ latent: rk | shared key part: dr ]  (row of the down projection)
 //   page[pos] = [ latent / sqrt(mean(latent^2) + eps) * w | rotate(shared part) ]         (one key "head" of rk + dr)
 //   q_full[h] = [ (left as it is: the absorbed plain part, rk) | rotate(q[h, dq:dq + dr]) ]   for every head
+//   q_exp[h]  = [ q[h, :dq] | rotate(q[h, dq:dq + dr]) ]                                       (optional)
 // rotate(): the first rd of the dr entries in rotate-half pairs (i, i + rd/2), angle pos * inv_freq[i] in fp32;
 // the other dr - rd entries pass.
 template <typename T>
 __global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_stride, const T* __restrict__ q,
                                       long long q_stride, T* __restrict__ q_full, long long qf_stride,
-                                      const float* __restrict__ norm_w, float eps, const float* __restrict__ inv_freq,
+                                      T* __restrict__ q_exp, long long qe_stride, const float* __restrict__ norm_w, float eps, const float* __restrict__ inv_freq,
                                       int rd, const int* __restrict__ positions, const int* __restrict__ row_seq,
                                       const int* __restrict__ block_table, int table_width, T* __restrict__ k_cache,
                                       int num_pages, int page_size, int num_seqs, int H, int dq, int dr, int rk,
@@ -233,7 +234,13 @@ __global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_str
       y = to_f32<T>(src[i]);
     }
     qf[(size_t)h * (rk + dr) + rk + i] = from_f32<T>(y);
+    if (q_exp) q_exp[(size_t)t * qe_stride + (size_t)h * (dq + dr) + dq + i] = from_f32<T>(y);
   }
+  if (q_exp)                                   // the queries whole, for attention against keys that are expanded per head
+    for (int idx = threadIdx.x; idx < H * dq; idx += blockDim.x) {
+      const int h = idx / dq, i = idx % dq;
+      q_exp[(size_t)t * qe_stride + (size_t)h * (dq + dr) + i] = qrow[(size_t)h * (dq + dr) + i];
+    }
   if (!k_cache) return;
   const T* row = kv + (size_t)t * kv_stride;
   float ss = 0.f;
@@ -263,7 +270,8 @@ __global__ void latent_prepare_kernel(const T* __restrict__ kv, long long kv_str
 }
 
 SI_EXPORT int si_latent_prepare(const void* kv, int dtype, long long kv_stride, const void* q, long long q_stride,
-                                void* q_full, long long qf_stride, const float* norm_w, float eps,
+                                void* q_full, long long qf_stride, void* q_exp, long long qe_stride,
+                                const float* norm_w, float eps,
                                 const float* inv_freq, int rd, const int* positions, const int* row_seq,
                                 const int* block_table, int table_width, void* k_cache, int num_pages, int page_size,
                                 int num_tokens, int num_seqs, int H, int dq, int dr, int rk, int* status,
@@ -272,12 +280,75 @@ SI_EXPORT int si_latent_prepare(const void* kv, int dtype, long long kv_stride, 
   if (rd < 0 || rd > dr || rd % 2) return -2;
   if (dtype == SI_BF16)
     si_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, stream, (const __nv_bfloat16*)kv,
-              kv_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)q_full, qf_stride, norm_w, eps, inv_freq,
+              kv_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)q_full, qf_stride, (__nv_bfloat16*)q_exp,
+              qe_stride, norm_w, eps, inv_freq,
               rd, positions, row_seq, block_table, table_width, (__nv_bfloat16*)k_cache, num_pages, page_size,
               num_seqs, H, dq, dr, rk, status);
   else
     si_launch(latent_prepare_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, (const float*)kv, kv_stride,
-              (const float*)q, q_stride, (float*)q_full, qf_stride, norm_w, eps, inv_freq, rd, positions, row_seq,
+              (const float*)q, q_stride, (float*)q_full, qf_stride, (float*)q_exp, qe_stride, norm_w, eps, inv_freq, rd,
+              positions, row_seq,
               block_table, table_width, (float*)k_cache, num_pages, page_size, num_seqs, H, dq, dr, rk, status);
+  return si_last_error();
+}
+
+// ---- the latent form expanded for long prompt portions -------------------------------------------------------
+// For the sequences listed in `seqs` ([E, 3] rows of (sequence of the step, first dense row, keys)), the cached
+// [latent | shared key part] rows of positions 0 .. keys-1 are copied out of the pages into consecutive dense rows,
+// where a matrix product can expand them into keys and values per head. One block per 8 keys of a sequence.
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ k_cache, const int* __restrict__ block_table, int table_width,
+                                     const int* __restrict__ seqs, T* __restrict__ dense, int num_pages, int page_size,
+                                     int num_seqs, int width, int* status) {
+  pdl_prologue();
+  const int e = blockIdx.y;
+  const int seq = seqs[3 * e], row0 = seqs[3 * e + 1], keys = seqs[3 * e + 2];
+  for (int j = blockIdx.x * 8; j < min(keys, blockIdx.x * 8 + 8); ++j) {
+    const long long page = page_of(block_table, table_width, num_pages, page_size, num_seqs, seq, j, status);
+    if (page < 0) continue;
+    const T* src = k_cache + ((size_t)page * page_size + j % page_size) * width;
+    T* dst = dense + (size_t)(row0 + j) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+SI_EXPORT int si_latent_gather(const void* k_cache, int dtype, const int* block_table, int table_width, const int* seqs,
+                               int num_listed, int max_keys, void* dense, int num_pages, int page_size, int num_seqs,
+                               int width, int* status, cudaStream_t stream) {
+  if (num_listed <= 0 || max_keys <= 0) return 0;
+  if (num_listed > 65535) return -2;
+  dim3 grid((max_keys + 7) / 8, num_listed);
+  if (dtype == SI_BF16)
+    si_launch(latent_gather_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)k_cache, block_table,
+              table_width, seqs, (__nv_bfloat16*)dense, num_pages, page_size, num_seqs, width, status);
+  else
+    si_launch(latent_gather_kernel<float>, grid, dim3(128), 0, stream, (const float*)k_cache, block_table, table_width, seqs,
+              (float*)dense, num_pages, page_size, num_seqs, width, status);
+  return si_last_error();
+}
+
+// keys[t, h, :] = [ plain[t, h*dq : (h+1)*dq] | dense[t, rk : rk + dr] ]: every head's expanded plain key part beside the
+// one rotated part that all heads share.
+template <typename T>
+__global__ void latent_expand_keys_kernel(const T* __restrict__ plain, const T* __restrict__ dense, T* __restrict__ keys,
+                                          int H, int dq, int dr, int rk) {
+  pdl_prologue();
+  const size_t t = blockIdx.x;
+  const int dk = dq + dr;
+  for (int idx = threadIdx.x; idx < H * dk; idx += blockDim.x) {
+    const int h = idx / dk, i = idx % dk;
+    keys[t * H * dk + idx] = i < dq ? plain[t * H * dq + (size_t)h * dq + i] : dense[t * (rk + dr) + rk + (i - dq)];
+  }
+}
+
+SI_EXPORT int si_latent_expand_keys(const void* plain, const void* dense, void* keys, int dtype, int rows, int H, int dq,
+                                    int dr, int rk, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dtype == SI_BF16)
+    si_launch(latent_expand_keys_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, (const __nv_bfloat16*)plain,
+              (const __nv_bfloat16*)dense, (__nv_bfloat16*)keys, H, dq, dr, rk);
+  else
+    si_launch(latent_expand_keys_kernel<float>, dim3(rows), dim3(256), 0, stream, (const float*)plain, (const float*)dense,
+              (float*)keys, H, dq, dr, rk);
   return si_last_error();
 }

@@ -878,13 +878,16 @@ def kv_store(qkv, positions, row_seq, block_table, k_cache, v_cache, page_size: 
 
 
 def latent_prepare(kv, q, q_full, norm_w, eps: float, inv_freq, rot_dims: int, positions, row_seq, block_table,
-                   k_cache, page_size: int, num_seqs: int, H: int, dq: int, dr: int, rk: int, status=None) -> None:
+                   k_cache, page_size: int, num_seqs: int, H: int, dq: int, dr: int, rk: int, status=None, q_exp=None) -> None:
     """The latent attention's step between its projections and the attention itself. ``kv`` [T, rk + dr]: the
     latent is normalised (weight ``norm_w``) and stored with the rotated shared key part as one key of rk + dr
     entries (``k_cache`` [pages, 1, page_size, rk + dr]; None: nothing stored). ``q`` [T, H * (dq + dr)]: every head's
     last dr entries are rotated into ``q_full[:, h, rk:]`` (``q_full`` [T, H * (rk + dr)]; its first rk entries per
-    head are the caller's). The first ``rot_dims`` of the dr entries are rotated in rotate-half pairs."""
-    _cuda(kv, q, q_full, norm_w, inv_freq, positions, row_seq, block_table, k_cache, status)
+    head are the caller's). The first ``rot_dims`` of the dr entries are rotated in rotate-half pairs. ``q_exp``
+    (optional, like ``q``) receives every head's [plain part | rotated part]."""
+    _cuda(kv, q, q_full, norm_w, inv_freq, positions, row_seq, block_table, k_cache, status, q_exp)
+    if q_exp is not None:
+        _need(q_exp.shape == q.shape and q_exp.dtype == q.dtype and q_exp.stride(1) == 1, "latent_prepare: q_exp must be like q")
     _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
     T = kv.shape[0]
     _need(kv.stride(1) == 1 and q.stride(1) == 1 and q_full.stride(1) == 1 and kv.shape[1] == rk + dr
@@ -898,9 +901,10 @@ def latent_prepare(kv, q, q_full, norm_w, eps: float, inv_freq, rot_dims: int, p
               "latent_prepare: the cache must be [pages, 1, page_size, rk + dr]")
         num_pages = k_cache.shape[0]
     f = _fn("attention_general", "si_latent_prepare",
-            [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_f, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p,
+            [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_f, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p,
              _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
-    _check(f(_ptr(kv), _dt(kv), kv.stride(0), _ptr(q), q.stride(0), _ptr(q_full), q_full.stride(0), _ptr(norm_w),
+    _check(f(_ptr(kv), _dt(kv), kv.stride(0), _ptr(q), q.stride(0), _ptr(q_full), q_full.stride(0), _ptr(q_exp),
+             q_exp.stride(0) if q_exp is not None else 0, _ptr(norm_w),
              float(eps), _ptr(inv_freq), int(rot_dims), _ptr(positions), _ptr(row_seq), _ptr(block_table),
              block_table.shape[1] if block_table is not None else 0, _ptr(k_cache), num_pages, page_size, T, num_seqs,
              H, dq, dr, rk, _ptr(status), _stream()), f"latent_prepare(rank={rk}, rot={dr})")
@@ -1088,3 +1092,31 @@ def gemm_heads(a, w, out, a_head: int, o_head: int) -> None:
     f = _fn("gemm_heads", "si_gemm_heads", [_c_p, _c_ll, _c_ll, _c_p, _c_p, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_ptr(a), a.stride(0), int(a_head), _ptr(w), _ptr(out), out.stride(0), int(o_head), M, H, N, K, _stream()),
            f"gemm_heads(M={M}, heads={H}, N={N}, K={K})")
+
+
+def latent_gather(k_cache, block_table, seqs, max_keys: int, dense, page_size: int, num_seqs: int, status=None) -> None:
+    """Copies the cached rows of positions 0 .. keys-1 of the listed sequences out of the pages into consecutive rows
+    of ``dense`` [rows, width]. ``seqs``: int32 [E, 3] rows of (sequence of the step, first dense row, keys);
+    ``max_keys``: the most keys of any of them. ``k_cache`` [pages, 1, page_size, width]."""
+    _cuda(k_cache, block_table, seqs, dense, status)
+    _i32(block_table, "block_table"); _i32(seqs, "seqs")
+    width = k_cache.shape[3]
+    _need(k_cache.is_contiguous() and k_cache.shape[1] == 1 and k_cache.shape[2] == page_size and dense.is_contiguous()
+          and dense.shape[1] == width and dense.dtype == k_cache.dtype and seqs.dim() == 2 and seqs.shape[1] == 3,
+          "latent_gather: cache [pages, 1, page_size, width], dense [rows, width], seqs [E, 3]")
+    f = _fn("attention_general", "si_latent_gather",
+            [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_ptr(k_cache), _dt(k_cache), _ptr(block_table), block_table.shape[1], _ptr(seqs), seqs.shape[0], int(max_keys),
+             _ptr(dense), k_cache.shape[0], page_size, int(num_seqs), width, _ptr(status), _stream()), "latent_gather")
+
+
+def latent_expand_keys(plain, dense, keys, H: int, dq: int, dr: int, rk: int) -> None:
+    """keys[t, h] = [plain[t, h*dq:(h+1)*dq] | dense[t, rk:rk+dr]] for every row t: per-head keys from the expanded plain
+    parts [rows, H*dq] and the shared rotated part that the gathered rows [rows, rk+dr] end with."""
+    _cuda(plain, dense, keys)
+    rows = plain.shape[0]
+    _need(plain.is_contiguous() and dense.is_contiguous() and keys.is_contiguous() and plain.shape == (rows, H * dq)
+          and dense.shape == (rows, rk + dr) and keys.numel() == rows * H * (dq + dr) and plain.dtype == dense.dtype == keys.dtype,
+          "latent_expand_keys: shapes or dtypes")
+    f = _fn("attention_general", "si_latent_expand_keys", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(plain), _ptr(dense), _ptr(keys), _dt(plain), rows, H, dq, dr, rk, _stream()), "latent_expand_keys")

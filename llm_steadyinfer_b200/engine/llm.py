@@ -62,6 +62,8 @@ class LLM:
         self.model = load_model(model, self.dtype, device) if isinstance(model, (str, bytes)) else model
         spec = self.model.spec
         self.max_seq_len = int(max_seq_len or spec.max_position)
+        if self.max_seq_len <= 0:
+            raise ValueError("this model's configuration names no position limit: give max_seq_len")
         if spec.max_position and self.max_seq_len > spec.max_position:
             raise ValueError(f"max_seq_len {self.max_seq_len} exceeds the model's max_position {spec.max_position}")
         self.max_batch = int(max_batch)

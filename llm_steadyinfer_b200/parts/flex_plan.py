@@ -17,8 +17,9 @@ MIN_KEYS_PER_SPLIT = 256
 BLOCKS_PER_SM = 2
 
 
-def plan(ctx, device, H: int, KV: int, dk: int, dv: int, own_v: bool, window) -> dict:
-    key = ("flex", H, KV, dk, dv, own_v, window)
+def plan(ctx, device, H: int, KV: int, dk: int, dv: int, own_v: bool, window, skip=frozenset()) -> dict:
+    """``skip``: sequences of the step that get no items (another path serves them)."""
+    key = ("flex", H, KV, dk, dv, own_v, window, tuple(sorted(skip)))
     got = ctx.plans.get(key)
     if got is not None:
         return got
@@ -26,6 +27,8 @@ def plan(ctx, device, H: int, KV: int, dk: int, dv: int, own_v: bool, window) ->
     dec, por = [], []
     qs, cl = ctx.h_q_start, ctx.h_ctx_len
     for s in range(ctx.num_seqs):
+        if s in skip:
+            continue
         row0, n = int(qs[s]), int(qs[s + 1] - qs[s])
         pos0 = int(cl[s]) - n
         if n <= per_item:
@@ -37,7 +40,7 @@ def plan(ctx, device, H: int, KV: int, dk: int, dv: int, own_v: bool, window) ->
     if fixed:                                         # fixed shapes: pad with empty items, shares by the shape alone
         dec += [(0, 0, 0, 0)] * (ctx.seq_cap - len(dec))
     out = {"dec": None, "por": None, "nsplit": 1, "scratch": None}
-    tag = f"{H}_{KV}_{dk}_{dv}_{int(own_v)}_{window}"
+    tag = f"{H}_{KV}_{dk}_{dv}_{int(own_v)}_{window}" + ("_rest" if skip else "")
     if dec:
         # blocks one item gets without shares: kv heads x parts of the query heads x slices of the value columns
         gb = max(g for g in range(1, min(H // KV, 64) + 1) if (H // KV) % g == 0)
@@ -51,6 +54,7 @@ def plan(ctx, device, H: int, KV: int, dk: int, dv: int, own_v: bool, window) ->
         if nsplit > 1:
             out["scratch"] = ctx.buf("flex_split", (ops.attn_flex_scratch_floats(len(dec), H, KV, dv, nsplit),), torch.float32)
     if por:
+        por.sort(key=lambda it: -(it[3] + it[2]))     # the items with most keys first: the last blocks to start are short
         out["por"] = ctx.upload_ints("flex_por_" + tag, np.asarray(por, dtype=np.int32)).view(-1, 4)
     ctx.plans[key] = out
     return out

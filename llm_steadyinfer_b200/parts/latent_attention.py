@@ -14,10 +14,18 @@ sum_j p_j W_uv,i c_j = W_uv,i (sum_j p_j c_j). Attention then runs with one shar
 entries whose first rk entries also serve as the value, for prompts and decoding alike, so a page holds
 (rk + dr) numbers a token whatever the head count.
 
+Long prompt portions in bfloat16 take the other way round, which costs a third of the arithmetic there (a head's
+key and value are dq + dr and dv wide instead of rk + dr and rk): the cached latents of the portion's sequence, all
+positions up to the portion's end, are copied out of the pages (``latent_gather``), expanded by two matrix products
+into per-head keys [W_uk,i c | k_rot] and values W_uv,i c, and ordinary multi-head attention with the sink runs over
+them with the whole queries. Which sequences of a step go which way is decided on the host in ``prepare`` (those
+that bring at least ``EXPAND_MIN_ROWS`` rows); both ways compute the same function, up to rounding.
+
 Tensor names below the part's prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, sink, o.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..csrc import ops
@@ -28,6 +36,7 @@ from .rotary import rotary_inverse_frequencies
 
 
 USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
+EXPAND_MIN_ROWS = 32         # sequences that bring at least this many rows attend to keys and values expanded per head
 
 
 class LatentAttention(Mixer):
@@ -80,6 +89,7 @@ class LatentAttention(Mixer):
         self.uq = t["uq"].contiguous()
         # per head the key up-projection transposed, [rk, dq]: q_lat = q_plain @ W_uk,i as a product with rows of W^T
         self.ukT = t["uk"].view(H, self.dq, self.rk).transpose(1, 2).contiguous()
+        self.uk = t["uk"].contiguous()                                        # as stored, for the expanded way
         self.uv = t["uv"].view(H, self.dv, self.rk).contiguous()
         self.o = t["o"].contiguous()
         self.q_norm = t["dq.norm"].contiguous()
@@ -100,9 +110,48 @@ class LatentAttention(Mixer):
         """Attention on the tensor cores: bfloat16 and sizes in multiples of 8."""
         return USE_TENSOR_CORES and self.dtype == torch.bfloat16 and ops.attn_flex_ok(self.H, 1, self.rk + self.dr, self.rk, False)
 
+    def expands(self) -> bool:
+        return (self.uses_flex() and EXPAND_MIN_ROWS > 0 and self.window is None
+                and ops.attn_flex_ok(self.H, self.H, self.dq + self.dr, self.dv, True))
+
     def prepare(self, ctx, cache):
-        if self.uses_flex() and cache.k is not None:
-            flex_plan.plan(ctx, self.device, self.H, 1, self.rk + self.dr, self.rk, False, self.window)
+        if not self.uses_flex() or cache.k is None:
+            return
+        key = ("latent_expand", self.H, self.dq, self.dr, self.dv, self.rk, self.window)
+        ex = ctx.plans.get(key)
+        if ex is None:
+            ex = ctx.plans[key] = self._plan_expanded(ctx)
+        if not ex["all"]:
+            flex_plan.plan(ctx, self.device, self.H, 1, self.rk + self.dr, self.rk, False, self.window, skip=ex["skip"])
+
+    def _plan_expanded(self, ctx) -> dict:
+        """Which sequences of the step attend the expanded way, where their gathered rows lie, and their work items."""
+        none = {"skip": frozenset(), "all": False, "total": 0}
+        if not self.expands() or ctx.seq_cap is not None:
+            return none
+        qs, cl = ctx.h_q_start, ctx.h_ctx_len
+        chosen = [s for s in range(ctx.num_seqs) if int(qs[s + 1] - qs[s]) >= EXPAND_MIN_ROWS]
+        if not chosen:
+            return none
+        per_item = ops.attn_flex_tokens(self.H, self.H)
+        seqs, items, total = [], [], 0
+        for e, s in enumerate(chosen):
+            row0, n, keys = int(qs[s]), int(qs[s + 1] - qs[s]), int(cl[s])
+            seqs.append((s, total, keys))
+            for b in range(0, n, per_item):
+                items.append((e, row0 + b, min(per_item, n - b), keys - n + b))
+            total += keys
+        items.sort(key=lambda it: -(it[3] + it[2]))
+        width = max(k for _, _, k in seqs)
+        tag = f"latent_exp_{self.H}_{self.dq}_{self.dr}_{self.dv}_{self.rk}"
+        both = ctx.upload_ints(tag, np.concatenate([np.asarray(seqs, dtype=np.int32).reshape(-1),
+                                                    np.asarray(items, dtype=np.int32).reshape(-1)]))
+        seqs_d, items_d = both[:3 * len(seqs)].view(-1, 3), both[3 * len(seqs):].view(-1, 4)
+        # the expanded rows are "pages" of one key: row j of sequence e is page first_row(e) + j
+        table = ctx.buf(tag + "_table", (len(seqs), width), torch.int32)
+        torch.add(seqs_d[:, 1:2], torch.arange(width, dtype=torch.int32, device=self.device).view(1, -1), out=table)
+        return {"skip": frozenset(chosen), "all": len(chosen) == ctx.num_seqs, "total": total, "seqs": seqs_d,
+                "items": items_d, "table": table, "width": width}
 
     def forward(self, x, ctx, cache):
         T = x.shape[0]
@@ -113,34 +162,64 @@ class LatentAttention(Mixer):
         ops.rmsnorm_rows(lat[:, :self.q_rank], self.q_norm, self.eps, cq)
         q = ctx.buf("lat_q", (T, H * (dq + dr)), self.dtype)
         linear(cq, self.uq, q, ctx.status)
+        ex = ctx.plans.get(("latent_expand", H, dq, dr, dv, rk, self.window)) if self.uses_flex() else None
+        expanded = ex is not None and ex["total"] > 0
+        absorbed = not (expanded and ex["all"])
         # queries against the cached latents: [W_uk,i^T q_plain,i | rotated part] per head
         q_full = ctx.buf("lat_qfull", (T, H * (rk + dr)), self.dtype)
-        if ops.gemm_heads_ok(q, self.ukT, q_full, H, dq + dr, rk + dr):          # few rows: all heads in one launch
+        q_exp = ctx.buf("lat_qexp", (T, H * (dq + dr)), self.dtype) if expanded else None
+        if not absorbed:
+            pass
+        elif ops.gemm_heads_ok(q, self.ukT, q_full, H, dq + dr, rk + dr):          # few rows: all heads in one launch
             ops.gemm_heads(q, self.ukT, q_full, dq + dr, rk + dr)
         else:
             for i in range(H):
                 linear(q[:, i * (dq + dr): i * (dq + dr) + dq], self.ukT[i], q_full[:, i * (rk + dr): i * (rk + dr) + rk], ctx.status)
         ops.latent_prepare(lat[:, self.q_rank:], q, q_full, self.kv_norm, self.eps, self.inv_freq, self.rot_dims,
                            ctx.positions, ctx.row_seq, cache.block_table, cache.k if cache.writes else None,
-                           cache.page_size, ctx.seq_slots, H, dq, dr, rk, status=ctx.status)
+                           cache.page_size, ctx.seq_slots, H, dq, dr, rk, status=ctx.status, q_exp=q_exp)
+        attn = ctx.buf("attn_out", (T, H * dv), self.dtype)
+        if absorbed:
+            self._attend_absorbed(q_full, attn, ctx, cache, ex["skip"] if expanded else frozenset())
+        if expanded:
+            self._attend_expanded(q_exp, attn, ctx, cache, ex)
+        out = ctx.buf("delta", (T, self.hidden), self.dtype)
+        linear(attn, self.o, out, ctx.status)
+        return out
+
+    def _attend_expanded(self, q_exp, attn, ctx, cache, ex):
+        """Multi-head attention of the chosen sequences' rows over keys and values expanded from the gathered latents."""
+        H, dq, dr, dv, rk = self.H, self.dq, self.dr, self.dv, self.rk
+        n = ex["total"]
+        dense = ctx.buf("lat_dense", (n, rk + dr), self.dtype)
+        ops.latent_gather(cache.k, cache.block_table, ex["seqs"], ex["width"], dense, cache.page_size, ctx.seq_slots,
+                          status=ctx.status)
+        plain = ctx.buf("lat_kplain", (n, H * dq), self.dtype)
+        linear(dense[:, :rk], self.uk, plain, ctx.status)
+        values = ctx.buf("lat_values", (n, H * dv), self.dtype)
+        linear(dense[:, :rk], self.uv.view(H * dv, rk), values, ctx.status)
+        keys = ctx.buf("lat_keys", (n, H * (dq + dr)), self.dtype)
+        ops.latent_expand_keys(plain, dense, keys, H, dq, dr, rk)
+        ops.attn_flex(q_exp, keys.view(n, H, 1, dq + dr), values.view(n, H, 1, dv), ex["table"], ex["items"], attn, 1,
+                      ex["table"].shape[0], H, H, dq + dr, dv, self.scale, 0, sink=self.sink, status=ctx.status)
+
+    def _attend_absorbed(self, q_full, attn, ctx, cache, skip):
+        T = q_full.shape[0]
+        H, dr, dv, rk = self.H, self.dr, self.dv, self.rk
         o_lat = ctx.buf("lat_olat", (T, H * rk), self.dtype)
         if self.uses_flex():
-            flex_plan.attend(flex_plan.plan(ctx, self.device, H, 1, rk + dr, rk, False, self.window), q_full, cache.k, None,
+            flex_plan.attend(flex_plan.plan(ctx, self.device, H, 1, rk + dr, rk, False, self.window, skip=skip), q_full, cache.k, None,
                              cache.block_table, o_lat, cache.page_size, ctx.seq_slots, H, 1, rk + dr, rk, self.scale,
                              self.window, sink=self.sink, status=ctx.status)
         else:
             ops.attention_general(q_full, cache.k, None, cache.block_table, ctx.row_seq, ctx.positions, o_lat, cache.page_size,
                                   ctx.seq_slots, H, 1, rk + dr, rk, self.scale, self.window or 0, sink=self.sink,
                                   status=ctx.status)
-        attn = ctx.buf("attn_out", (T, H * dv), self.dtype)
         if ops.gemm_heads_ok(o_lat, self.uv, attn, H, rk, dv):
             ops.gemm_heads(o_lat, self.uv, attn, rk, dv)
         else:
             for i in range(H):
                 linear(o_lat[:, i * rk:(i + 1) * rk], self.uv[i], attn[:, i * dv:(i + 1) * dv], ctx.status)
-        out = ctx.buf("delta", (T, self.hidden), self.dtype)
-        linear(attn, self.o, out, ctx.status)
-        return out
 
 
 register_mixer("latent_attention", LatentAttention)

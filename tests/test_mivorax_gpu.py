@@ -408,3 +408,22 @@ def test_per_head_product(M, H, N, K, a_head, o_head):
         assert (out[:, h * o_head:h * o_head + N].float() - want).abs().max().item() <= 2e-2
     if o_head > N:
         assert (out[:, N:o_head] == 7.0).all()            # nothing written between the heads
+
+
+def test_command_line_serves_the_design(folders, tmp_path):
+    """The serving program on a Mivorax folder: requests of random lengths arriving over time, sampling, a pool that
+    is used again; and once more on random weights drawn from a configuration file."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "m.json"
+    common = ["--num-requests", "12", "--max-batch", "4", "--max-gen", "10", "--prompt-len-dist", "lognormal:30,0.7,2,90",
+              "--output-len-dist", "lognormal:6,0.5,1,10", "--request-rate", "300", "--temperature", "0.8", "--top-p", "0.9",
+              "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "60", "--max-num-batched-tokens", "40",
+              "--max-model-len", "128", "--output-json", str(out)]
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(mc.MIXED_B))
+    for source in (["--checkpoint", folders["mixed_a"]], ["--model-config", str(cfg_file)]):
+        proc = subprocess.run([sys.executable, os.path.join(root, "bin", "offline_batch_benchmark"), *source, *common],
+                              capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        m = json.loads(out.read_text())[0]
+        assert m["completed"] == 12 and m["rejected"] == 0 and m["output_tokens"] > 12 and m["output_tps"] > 0
