@@ -80,47 +80,53 @@ attn_flex_kernel(const FlexParams p) {
   const int dk_chunks = p.dk / 8;
   const int kt_steps = (p.dk + 15) / 16;
 
+  // A thread fetches chunks of one key row per tile (THREADS / BLOCK_N threads share a row), so that the row's
+  // page is looked up once per thread and tile; the copies that follow do not wait for one another.
+  constexpr int TPR = THREADS / BLOCK_N;
   auto load_kv = [&](int j0, int stage) {
     bf16* Kt = Ks + (size_t)stage * BLOCK_N * p.dk_pitch;
-    for (int id = threadIdx.x; id < BLOCK_N * kch; id += THREADS) {
-      const int row = id / kch, c = id % kch;
-      const int j = j0 + row;
-      bool valid = j >= kv_lo && j < kv_end && c < dk_chunks;
-      size_t off = 0;
-      if (valid) {
-        const int slot = j / p.page_size;
-        const int page = slot < p.table_width ? table[slot] : -1;
-        if (page < 0 || page >= p.num_pages) {
-          set_status(p.status, SI_BAD_PAGE);
-          valid = false;
-        } else {
-          off = (((size_t)page * p.KV + g) * p.page_size + (j - slot * p.page_size)) * p.dk + c * 8;
-        }
+    const int row = threadIdx.x / TPR, c_first = threadIdx.x % TPR;
+    const int j = j0 + row;
+    bool in_range = j >= kv_lo && j < kv_end;
+    size_t tok = 0;
+    if (in_range) {
+      const int slot = j / p.page_size;
+      const int page = slot < p.table_width ? table[slot] : -1;
+      if (page < 0 || page >= p.num_pages) {
+        set_status(p.status, SI_BAD_PAGE);
+        in_range = false;
+      } else {
+        tok = ((size_t)page * p.KV + g) * p.page_size + (j - slot * p.page_size);
       }
-      cp_async16(ftile(Kt, kch, row, c), p.k_cache + off, valid);
+    }
+    const bf16* krow = p.k_cache + tok * p.dk;
+    for (int c = c_first; c < kch; c += TPR) {
+      const bool valid = in_range && c < dk_chunks;
+      cp_async16(ftile(Kt, kch, row, c), valid ? krow + c * 8 : p.k_cache, valid);
     }
     if (own_v) {
       bf16* Vt = Vs + (size_t)stage * BLOCK_N * DVB;
-      for (int id = threadIdx.x; id < BLOCK_N * DT; id += THREADS) {
-        const int row = id / DT, c = id % DT;
-        const int j = j0 + row;
-        bool valid = j >= kv_lo && j < kv_end && v0 + c * 8 < p.dv;
-        size_t off = 0;
-        if (valid) {
-          const int slot = j / p.page_size;
-          const int page = slot < p.table_width ? table[slot] : -1;
-          if (page < 0 || page >= p.num_pages) valid = false;
-          else off = (((size_t)page * p.KV + g) * p.page_size + (j - slot * p.page_size)) * p.dv + v0 + c * 8;
-        }
-        cp_async16(ftile(Vt, DT, row, c), p.v_cache + off, valid);
+      const bf16* vrow = p.v_cache + tok * p.dv + v0;
+      for (int c = c_first; c < DT; c += TPR) {
+        const bool valid = in_range && v0 + c * 8 < p.dv;
+        cp_async16(ftile(Vt, DT, row, c), valid ? vrow + c * 8 : p.v_cache, valid);
       }
     }
     if (p.bias_in_smem) {                     // entry (d - dlo, head) with dlo the least distance of the tile
       float* Bt = Bs + (size_t)stage * bwin * p.Gb;
       const int dlo = item.pos0 - (j0 + BLOCK_N - 1);
-      for (int id = threadIdx.x; id < bwin * p.Gb; id += THREADS) {
-        const int d = dlo + id / p.Gb;
-        Bt[id] = d < 0 ? 0.f : p.dist_bias[(size_t)min(d, p.nd - 1) * p.H + head0 + id % p.Gb] * LOG2E;
+      const int total = bwin * p.Gb;
+      for (int id0 = threadIdx.x; id0 < total; id0 += 4 * THREADS) {        // four loads in flight, then four stores
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int id = id0 + u * THREADS;
+          const int d = dlo + id / p.Gb;
+          v[u] = (id < total && d >= 0) ? p.dist_bias[(size_t)min(d, p.nd - 1) * p.H + head0 + id % p.Gb] * LOG2E : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (id0 + u * THREADS < total) Bt[id0 + u * THREADS] = v[u];
       }
     }
   };

@@ -116,12 +116,20 @@ SI_EXPORT int si_causal_conv(const void* u, int dtype, long long u_stride, const
 }
 
 // ---- the recurrence -------------------------------------------------------------------------------------------
-// One block per (sequence of the step, head). Thread (p, ns) keeps NPT entries of column p of the state in
-// registers, in groups of four neighbouring n: entry i is S[((i / 4) * NS + ns) * 4 + i % 4, p], so that the NS
-// threads of one p (neighbouring lanes) read B and C from shared memory as consecutive 16-byte words, without bank
-// conflicts; they add their parts of y_t with shuffles. Tokens are walked in order, SCAN_CHUNK at a time staged in
-// shared memory (B, C, x, step size, decay).
+// One block per (sequence of the step, head, cut of the columns). Thread (p, ns) keeps NPT entries of column p of
+// the state in registers, in groups of four neighbouring n: entry i is S[((i / 4) * NS + ns) * 4 + i % 4, p], so that
+// the NS threads of one p (neighbouring lanes) read B and C from shared memory as consecutive 16-byte words, without
+// bank conflicts; they add their parts of y_t with shuffles. Tokens are walked in order, SCAN_CHUNK at a time; the
+// chunk after the one being computed is on its way into the other half of shared memory meanwhile (cp.async for B,
+// C and x; step size and decay by the first threads).
 #define SCAN_CHUNK 32
+
+__device__ __forceinline__ void scan_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void scan_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
 
 template <typename T, int NPT>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_stride,     // conv output: [x | B | C]
@@ -139,12 +147,10 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
   const int pos0 = ctx_len[s] - n_rows;
   const int g = h / (heads / groups);
   const int inner = heads * P;
-  float* sB = sm;                              // [SCAN_CHUNK][Npad]
   const int Npad = NS * NPT;
-  float* sC = sB + SCAN_CHUNK * Npad;
-  float* sX = sC + SCAN_CHUNK * Npad;          // [SCAN_CHUNK][Pb], already times the step size
-  float* sXr = sX + SCAN_CHUNK * Pb;           // [SCAN_CHUNK][Pb], as it came (for the skip term)
-  float* sDec = sXr + SCAN_CHUNK * Pb;         // [2][SCAN_CHUNK] decay, step size
+  const int Pbp = (Pb + 3) / 4 * 4;
+  // two halves of [ B: CHUNK x Npad | C: CHUNK x Npad | x: CHUNK x Pbp | decay: CHUNK | step: CHUNK ]
+  const int half_floats = 2 * SCAN_CHUNK * Npad + SCAN_CHUNK * Pbp + 2 * SCAN_CHUNK;
   const int tid = threadIdx.x;
   // the block's columns of the state: [p0, p0 + Pb) (blockIdx.z cuts P where that gives the device more blocks)
   const int p0 = blockIdx.z * Pb;
@@ -152,7 +158,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
   const bool live = tid / NS < Pb && p0 + tid / NS < P;      // threads beyond the columns follow idly
   const int p = live ? p0 + tid / NS : p0;
   const int gtid = p * NS + ns;            // the thread's place in the head's state, whatever the cut
-  // the head's state in the order of the threads: entry i of thread tid at i * (P * NS) + tid
+  // the head's state in the order of the threads: entry i of thread gtid at i * (P * NS) + gtid
   float* st = state + (size_t)slots[s] * state_stride + (size_t)h * Npad * P;
   const int held = P * NS;
   float S[NPT];
@@ -161,47 +167,87 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
   const float rate = expf(a_log[h]);
   const float bias = dt_bias[h];
   const float dskip = Dskip[h];
-  for (int c0 = 0; c0 < n_rows; c0 += SCAN_CHUNK) {
+  for (int idx = tid; idx < 2 * half_floats; idx += blockDim.x) sm[idx] = 0.f;      // the padding stays zero
+  __syncthreads();
+  // 16-byte copies where every source address is a multiple of 16 bytes
+  const bool vec = (xbc_stride % 4 == 0) && (inner % 4 == 0) && (N % 4 == 0) && (P % 4 == 0) && (Pb % 4 == 0)
+                   && ((size_t)xbc % 16 == 0);
+  const int pcols = min(Pb, P - p0);
+
+  auto stage = [&](int c0, int buf) {
     const int cn = min(SCAN_CHUNK, n_rows - c0);
-    __syncthreads();
-    for (int idx = tid; idx < cn; idx += blockDim.x) {
-      const float dt = softplus_f(to_f32<T>(dt_raw[(size_t)(row0 + c0 + idx) * dt_stride + h]) + bias);
-      sDec[idx] = expf(-rate * dt);
-      sDec[SCAN_CHUNK + idx] = dt;
-    }
-    for (int idx = tid; idx < cn * Npad; idx += blockDim.x) {
-      const int r = idx / Npad, n = idx % Npad;
-      const float* src = xbc + (size_t)(row0 + c0 + r) * xbc_stride + inner + (size_t)g * N;
-      sB[idx] = n < N ? src[n] : 0.f;
-      sC[idx] = n < N ? src[(size_t)groups * N + n] : 0.f;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < cn * Pb; idx += blockDim.x) {
-      const int r = idx / Pb, pp = idx % Pb;
-      const float x = p0 + pp < P ? xbc[(size_t)(row0 + c0 + r) * xbc_stride + (size_t)h * P + p0 + pp] : 0.f;
-      sXr[idx] = x;
-      sX[idx] = x * sDec[SCAN_CHUNK + r];
-    }
-    __syncthreads();
-    {
-      for (int r = 0; r < cn; ++r) {
-        const float dec = sDec[r];
-        const float dx = sX[r * Pb + p - p0];
-        const float4* Br = reinterpret_cast<const float4*>(sB + r * Npad) + ns;
-        const float4* Cr = reinterpret_cast<const float4*>(sC + r * Npad) + ns;
-        float acc = 0.f;
-#pragma unroll
-        for (int i4 = 0; i4 < NPT / 4; ++i4) {
-          const float4 b = Br[i4 * NS], c = Cr[i4 * NS];
-          S[4 * i4 + 0] = fmaf(dec, S[4 * i4 + 0], dx * b.x); acc = fmaf(S[4 * i4 + 0], c.x, acc);
-          S[4 * i4 + 1] = fmaf(dec, S[4 * i4 + 1], dx * b.y); acc = fmaf(S[4 * i4 + 1], c.y, acc);
-          S[4 * i4 + 2] = fmaf(dec, S[4 * i4 + 2], dx * b.z); acc = fmaf(S[4 * i4 + 2], c.z, acc);
-          S[4 * i4 + 3] = fmaf(dec, S[4 * i4 + 3], dx * b.w); acc = fmaf(S[4 * i4 + 3], c.w, acc);
-        }
-        for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, NS);
-        if (ns == 0 && live) y[(size_t)(row0 + c0 + r) * y_stride + (size_t)h * P + p] = acc + dskip * sXr[r * Pb + p - p0];
+    float* hB = sm + (size_t)buf * half_floats;
+    float* hC = hB + SCAN_CHUNK * Npad;
+    float* hX = hC + SCAN_CHUNK * Npad;
+    float* hDec = hX + SCAN_CHUNK * Pbp;
+    const float* base = xbc + (size_t)(row0 + c0) * xbc_stride;
+    if (vec) {
+      const int nq = N / 4, pq = pcols / 4;
+      for (int idx = tid; idx < cn * nq; idx += blockDim.x) {
+        const int r = idx / nq, q = idx % nq;
+        const float* src = base + (size_t)r * xbc_stride + inner + (size_t)g * N + 4 * q;
+        scan_cp16(hB + r * Npad + 4 * q, src);
+        scan_cp16(hC + r * Npad + 4 * q, src + (size_t)groups * N);
+      }
+      for (int idx = tid; idx < cn * pq; idx += blockDim.x) {
+        const int r = idx / pq, q = idx % pq;
+        scan_cp16(hX + r * Pbp + 4 * q, base + (size_t)r * xbc_stride + (size_t)h * P + p0 + 4 * q);
+      }
+    } else {
+      for (int idx = tid; idx < cn * N; idx += blockDim.x) {
+        const int r = idx / N, n = idx % N;
+        const float* src = base + (size_t)r * xbc_stride + inner + (size_t)g * N + n;
+        scan_cp4(hB + r * Npad + n, src);
+        scan_cp4(hC + r * Npad + n, src + (size_t)groups * N);
+      }
+      for (int idx = tid; idx < cn * pcols; idx += blockDim.x) {
+        const int r = idx / pcols, pp = idx % pcols;
+        scan_cp4(hX + r * Pbp + pp, base + (size_t)r * xbc_stride + (size_t)h * P + p0 + pp);
       }
     }
+    asm volatile("cp.async.commit_group;\n" ::);
+    for (int idx = tid; idx < cn; idx += blockDim.x) {
+      const float dt = softplus_f(to_f32<T>(dt_raw[(size_t)(row0 + c0 + idx) * dt_stride + h]) + bias);
+      hDec[idx] = expf(-rate * dt);
+      hDec[SCAN_CHUNK + idx] = dt;
+    }
+  };
+
+  stage(0, 0);
+  int buf = 0;
+  for (int c0 = 0; c0 < n_rows; c0 += SCAN_CHUNK, buf ^= 1) {
+    const int cn = min(SCAN_CHUNK, n_rows - c0);
+    if (c0 + SCAN_CHUNK < n_rows) {
+      stage(c0 + SCAN_CHUNK, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+    const float* hB = sm + (size_t)buf * half_floats;
+    const float* hC = hB + SCAN_CHUNK * Npad;
+    const float* hX = hC + SCAN_CHUNK * Npad;
+    const float* hDec = hX + SCAN_CHUNK * Pbp;
+    for (int r = 0; r < cn; ++r) {
+      const float dec = hDec[r];
+      const float xr = hX[r * Pbp + p - p0];
+      const float dx = xr * hDec[SCAN_CHUNK + r];
+      const float4* Br = reinterpret_cast<const float4*>(hB + r * Npad) + ns;
+      const float4* Cr = reinterpret_cast<const float4*>(hC + r * Npad) + ns;
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < NPT / 4; ++i4) {
+        const float4 b = Br[i4 * NS], c = Cr[i4 * NS];
+        S[4 * i4 + 0] = fmaf(dec, S[4 * i4 + 0], dx * b.x); acc0 = fmaf(S[4 * i4 + 0], c.x, acc0);
+        S[4 * i4 + 1] = fmaf(dec, S[4 * i4 + 1], dx * b.y); acc1 = fmaf(S[4 * i4 + 1], c.y, acc1);
+        S[4 * i4 + 2] = fmaf(dec, S[4 * i4 + 2], dx * b.z); acc0 = fmaf(S[4 * i4 + 2], c.z, acc0);
+        S[4 * i4 + 3] = fmaf(dec, S[4 * i4 + 3], dx * b.w); acc1 = fmaf(S[4 * i4 + 3], c.w, acc1);
+      }
+      float acc = acc0 + acc1;
+      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, NS);
+      if (ns == 0 && live) y[(size_t)(row0 + c0 + r) * y_stride + (size_t)h * P + p] = acc + dskip * xr;
+    }
+    __syncthreads();       // everyone is done with this half before it is filled again
   }
   if (live) {
 #pragma unroll
@@ -222,7 +268,8 @@ static int scan_launch(const float* xbc, long long xbc_stride, const void* dt_ra
   int Pb = P;
   while (Pb % 2 == 0 && Pb / 2 >= 8 && 2LL * num_seqs * heads * (P / Pb) <= si_sm_count()) Pb /= 2;
   int threads = (Pb * NS + 31) / 32 * 32;
-  const size_t smem = (size_t)(2 * SCAN_CHUNK * NS * NPT + 2 * SCAN_CHUNK * Pb + 2 * SCAN_CHUNK) * sizeof(float);
+  const size_t smem = (size_t)2 * (2 * SCAN_CHUNK * NS * NPT + SCAN_CHUNK * ((Pb + 3) / 4 * 4) + 2 * SCAN_CHUNK) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
   if (smem > 48 * 1024) {
     if (cudaFuncSetAttribute(ssm_scan_kernel<T, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return -2;
