@@ -27,6 +27,8 @@ struct FlexParams {
   const float* sink;                             // fp32 [H] or nullptr
   int num_pages, page_size, num_seqs, H, KV, G, Gb, hparts, dk, dv, dk_pitch;
   int bias_in_smem;         // the distances a key tile can meet are staged in shared memory, tile by tile
+  int warps_are_slices;     // items of at most 16 rows whose values are key columns: every warp takes rows 0..15 and a
+                            // value slice of its own, so that a block serves four slices from one key tile
   float scale_log2;         // scale * log2(e)
   int window, nsplit;
   int* status;
@@ -58,8 +60,9 @@ attn_flex_kernel(const FlexParams p) {
   const int item_idx = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
   const AttnItem item = p.items[item_idx];
   const int g = blockIdx.y / p.hparts, hpart = blockIdx.y % p.hparts;
-  const int v0 = blockIdx.z * DVB;                      // first value column of this block
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wrow = p.warps_are_slices ? 0 : (threadIdx.x >> 5) * 16;          // first tile row of this warp
+  const int v0 = (p.warps_are_slices ? blockIdx.z * 4 + (threadIdx.x >> 5) : blockIdx.z) * DVB;   // first value column
+  const int lane = threadIdx.x & 31;
   if (item.ntok <= 0) return;
   if (item.seq < 0 || item.seq >= p.num_seqs) {
     if (threadIdx.x == 0) set_status(p.status, SI_BAD_SEQ);
@@ -144,15 +147,15 @@ attn_flex_kernel(const FlexParams p) {
   }
   cp_async_commit();
 
-  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const int r_lo = wrow + (lane >> 2), r_hi = r_lo + 8;
   const int tok_lo = r_lo / p.Gb, tok_hi = r_hi / p.Gb;
   const int pos_lo = tok_lo < item.ntok ? item.pos0 + tok_lo : -1;     // -1: row unused
   const int pos_hi = tok_hi < item.ntok ? item.pos0 + tok_hi : -1;
   const int hh_lo = r_lo % p.Gb, hh_hi = r_hi % p.Gb;
   const int head_lo = head0 + hh_lo, head_hi = head0 + hh_hi;
-  const int warp_last_tok = min(item.ntok - 1, (warp * 16 + 15) / p.Gb);
-  const int warp_first_tok = (warp * 16) / p.Gb;
-  const bool warp_active = warp_first_tok < item.ntok;
+  const int warp_last_tok = min(item.ntok - 1, (wrow + 15) / p.Gb);
+  const int warp_first_tok = wrow / p.Gb;
+  const bool warp_active = warp_first_tok < item.ntok && v0 < p.dv;
   const int warp_max_pos = item.pos0 + warp_last_tok;
   const int warp_min_pos = item.pos0 + warp_first_tok;
 
@@ -178,10 +181,10 @@ attn_flex_kernel(const FlexParams p) {
       float s[NT][4];
 #pragma unroll
       for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll 2
+#pragma unroll 4
       for (int kk = 0; kk < kt_steps; ++kk) {
         unsigned a0, a1, a2, a3;
-        ldsm_x4(a0, a1, a2, a3, ftile(Qs, kch, warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
+        ldsm_x4(a0, a1, a2, a3, ftile(Qs, kch, wrow + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
 #pragma unroll
         for (int nt = 0; nt < NT; nt += 2) {
           unsigned b0, b1, b2, b3;
@@ -265,7 +268,7 @@ attn_flex_kernel(const FlexParams p) {
     for (int half = 0; half < 2; ++half) {
       const int r = half ? r_hi : r_lo;
       if (r / p.Gb >= item.ntok) continue;
-      if ((lane & 3) == 0 && blockIdx.z == 0) {
+      if ((lane & 3) == 0 && v0 == 0) {
         pml[r * 2] = half ? m_hi : m_lo;
         pml[r * 2 + 1] = half ? l_hi : l_lo;
       }
@@ -371,7 +374,7 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
                            const int* block_table, int table_width, const int* items, int num_items, void* out,
                            long long out_stride, int num_pages, int page_size, int num_seqs, int H, int KV, int dk,
                            int dv, float scale, int window, const float* dist_bias, int nd, const float* sink,
-                           int nsplit, float* scratch, int* status, cudaStream_t stream) {
+                           int nsplit, float* scratch, int max_rows, int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (!si_attn_flex_ok(H, KV, dk, dv, v_cache != nullptr) || nsplit < 1 || nsplit > 64 || (nsplit > 1 && !scratch)) return -2;
   FlexParams p;
@@ -392,14 +395,18 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
   const int block_n = p.dk_pitch > 256 ? 32 : 64;        // the two key stages and the queries share 227 KB
   const int dvb = dv > 64 ? 128 : 64;
   const int dslices = (dv + dvb - 1) / dvb;
+  // items of at most 16 rows (max_rows, 0: unknown) over keys that are their own values: the four warps take a value
+  // slice each instead of 16 rows each
+  p.warps_are_slices = (!own_v && dslices > 1 && max_rows > 0 && max_rows <= 16) ? 1 : 0;
+  const int zblocks = p.warps_are_slices ? (dslices + 3) / 4 : dslices;
   size_t smem = ((size_t)(FLEX_M + 2 * block_n) * p.dk_pitch + (own_v ? (size_t)2 * block_n * dvb : 0)) * sizeof(bf16);
   if (smem > 227 * 1024) return -2;
   const size_t bias_bytes = (size_t)2 * (block_n + FLEX_M / p.Gb) * p.Gb * sizeof(float);
   p.bias_in_smem = dist_bias && smem + bias_bytes <= 227 * 1024 ? 1 : 0;       // else each score fetches its own
   if (p.bias_in_smem) smem += bias_bytes;
   int rc;
-  if (block_n == 64) rc = dvb == 128 ? flex_launch<64, 128>(p, dslices, smem, stream) : flex_launch<64, 64>(p, dslices, smem, stream);
-  else rc = dvb == 128 ? flex_launch<32, 128>(p, dslices, smem, stream) : flex_launch<32, 64>(p, dslices, smem, stream);
+  if (block_n == 64) rc = dvb == 128 ? flex_launch<64, 128>(p, zblocks, smem, stream) : flex_launch<64, 64>(p, zblocks, smem, stream);
+  else rc = dvb == 128 ? flex_launch<32, 128>(p, zblocks, smem, stream) : flex_launch<32, 64>(p, zblocks, smem, stream);
   if (rc) return rc;
   if (nsplit > 1) {
     attn_flex_merge_kernel<<<dim3(num_items, KV * p.hparts, FLEX_M), 128, 0, stream>>>(p);

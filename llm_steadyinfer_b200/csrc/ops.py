@@ -1034,10 +1034,12 @@ def attn_flex_scratch_floats(num_items: int, H: int, KV: int, dv: int, nsplit: i
 
 def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int, dk: int,
               dv: int, scale: float, window: int = 0, dist_bias=None, sink=None, nsplit: int = 1, scratch=None,
-              status=None) -> None:
+              status=None, max_rows: int = 0) -> None:
     """``attention_general`` on the tensor cores for bfloat16. ``items``: int32 [n, 4] rows (sequence, first row,
     tokens, first position) of at most ``attn_flex_tokens`` tokens. ``nsplit`` > 1 cuts every item's keys into that
-    many shares (decode rows over long contexts); ``scratch`` then holds ``attn_flex_scratch_floats`` floats."""
+    many shares (decode rows over long contexts); ``scratch`` then holds ``attn_flex_scratch_floats`` floats.
+    ``max_rows``: the most rows (tokens x query heads of a key head served together) of any item when the caller knows it
+    (0: unknown); at most 16 rows over keys that are their own values let a block's warps take a value slice each."""
     _cuda(q, k_cache, v_cache, block_table, items, out, dist_bias, sink, scratch, status)
     _i32(block_table, "block_table"); _i32(items, "items")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
@@ -1064,10 +1066,10 @@ def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_
               f"attn_flex: scratch must hold {need} floats")
     f = _fn("attention_flex", "si_attn_flex",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p])
+             _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p])
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(items),
              items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs, H, KV, dk, dv,
-             float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), _ptr(status),
+             float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), int(max_rows), _ptr(status),
              _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
 
 

@@ -266,7 +266,12 @@ static int scan_launch(const float* xbc, long long xbc_stride, const void* dt_ra
   // sequence of 2,048 rows: 64 blocks 1.37 ms, 512 blocks of 8 columns 4.26 ms). The state's layout does not
   // depend on the cut.
   int Pb = P;
-  while (Pb % 2 == 0 && Pb / 2 >= 8 && 2LL * num_seqs * heads * (P / Pb) <= si_sm_count()) Pb /= 2;
+  static int per_sm = 0;
+  if (per_sm == 0) {
+    const char* e = getenv("SI_SCAN_BLOCKS_PER_SM");
+    per_sm = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 1;
+  }
+  while (Pb % 2 == 0 && Pb / 2 >= 8 && 2LL * num_seqs * heads * (P / Pb) <= (long long)per_sm * si_sm_count()) Pb /= 2;
   int threads = (Pb * NS + 31) / 32 * 32;
   const size_t smem = (size_t)2 * (2 * SCAN_CHUNK * NS * NPT + SCAN_CHUNK * ((Pb + 3) / 4 * 4) + 2 * SCAN_CHUNK) * sizeof(float);
   if (smem > 200 * 1024) return -2;

@@ -39,12 +39,17 @@ def plan(ctx, device, H: int, KV: int, dk: int, dv: int, own_v: bool, window, sk
     fixed = ctx.seq_cap is not None
     if fixed:                                         # fixed shapes: pad with empty items, shares by the shape alone
         dec += [(0, 0, 0, 0)] * (ctx.seq_cap - len(dec))
-    out = {"dec": None, "por": None, "nsplit": 1, "scratch": None}
+    out = {"dec": None, "por": None, "nsplit": 1, "scratch": None, "dec_rows": 0}
     tag = f"{H}_{KV}_{dk}_{dv}_{int(own_v)}_{window}" + ("_rest" if skip else "")
     if dec:
         # blocks one item gets without shares: kv heads x parts of the query heads x slices of the value columns
         gb = max(g for g in range(1, min(H // KV, 64) + 1) if (H // KV) % g == 0)
-        per = KV * ((H // KV) // gb) * -(-dv // (128 if dv > 64 else 64))
+        slices = -(-dv // (128 if dv > 64 else 64))
+        # the most rows of any item; in a fixed shape every item is one token
+        out["dec_rows"] = gb * (1 if fixed else max(d[2] for d in dec))
+        if not own_v and slices > 1 and out["dec_rows"] <= 16:
+            slices = -(-slices // 4)                  # a block's four warps take a slice each
+        per = KV * ((H // KV) // gb) * slices
         nsplit = max(1, min(MAX_SPLITS, BLOCKS_PER_SM * ops.sm_count(device) // (len(dec) * per)))
         if not fixed:
             longest = max(d[3] + d[2] for d in dec)
@@ -65,6 +70,6 @@ def attend(pl: dict, q, k_cache, v_cache, block_table, out, page_size, seq_slots
     args = (page_size, seq_slots, H, KV, dk, dv, scale, window or 0)
     if pl["dec"] is not None:
         ops.attn_flex(q, k_cache, v_cache, block_table, pl["dec"], out, *args, dist_bias=dist_bias, sink=sink,
-                      nsplit=pl["nsplit"], scratch=pl["scratch"], status=status)
+                      nsplit=pl["nsplit"], scratch=pl["scratch"], status=status, max_rows=pl["dec_rows"])
     if pl["por"] is not None:
         ops.attn_flex(q, k_cache, v_cache, block_table, pl["por"], out, *args, dist_bias=dist_bias, sink=sink, status=status)

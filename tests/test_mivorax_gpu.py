@@ -242,7 +242,7 @@ def test_attention_kernels_far_keys_and_edges(case, kernel, dtype):
 
 
 @pytest.mark.parametrize("H,KV,dk,dv,own_v", [(8, 2, 64, 32, True), (4, 1, 48, 80, True), (16, 1, 160, 128, False),
-                                              (128, 1, 72, 64, False), (6, 3, 192, 160, True), (2, 1, 576, 512, False)])
+                                              (128, 1, 72, 64, False), (6, 3, 192, 160, True), (2, 1, 576, 512, False), (16, 1, 320, 288, False)])
 def test_tensor_core_attention_sizes(H, KV, dk, dv, own_v):
     """The tensor-core kernel against the plain one at head layouts that take its different routes: value slices, key
     tiles of 32, more heads than a tile has rows, sizes that are no multiple of 16."""
@@ -268,7 +268,14 @@ def test_tensor_core_attention_sizes(H, KV, dk, dv, own_v):
     ones = torch.tensor([(0, r, 1, r) for r in range(n)], dtype=torch.int32, device=dev)
     scratch = torch.zeros(ops.attn_flex_scratch_floats(n, H, KV, dv, 3), dtype=torch.float32, device=dev)
     got.zero_()
-    ops.attn_flex(q, kc.to(dev), vc, table.to(dev), ones, got, ps, 1, H, KV, dk, dv, dk ** -0.5, 0, dist_bias=bias, sink=sink, nsplit=3, scratch=scratch)
+    # single rows with key shares; the caller says how many rows an item has at most (few rows over keys that are
+    # their own values: the warps take a value slice each)
+    ops.attn_flex(q, kc.to(dev), vc, table.to(dev), ones, got, ps, 1, H, KV, dk, dv, dk ** -0.5, 0, dist_bias=bias, sink=sink, nsplit=3,
+                  scratch=scratch, max_rows=min(H // KV, 64))
+    assert (got.float() - want.float()).abs().max().item() <= 2e-2
+    got.zero_()
+    ops.attn_flex(q, kc.to(dev), vc, table.to(dev), ones, got, ps, 1, H, KV, dk, dv, dk ** -0.5, 0, dist_bias=bias, sink=sink,
+                  max_rows=min(H // KV, 64))
     assert (got.float() - want.float()).abs().max().item() <= 2e-2
 
 
