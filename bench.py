@@ -323,6 +323,19 @@ def mivorax_section(args) -> int:
         for i in range(W):
             decode(i)
         runner.check_status()
+        if args.profiler_range:
+            # one prompt step and one direct decode step of this model between cudaProfilerStart/Stop, for a launch list
+            # (ncu --profile-from-start off); nothing is timed
+            entries = [StepEntry(r, [toks[state["i"]][j]], [0]) for j, r in enumerate(ids)]
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStart()
+            prefill(0)
+            runner.step(entries)
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStop()
+            runner.check_status()
+            print(json.dumps({"section": "mivorax", "profiled": name, "prefill_tokens": PT, "decode_batch": B, "decode_context": CTX}))
+            return 0
         dec_ms = timed_each(decode, K)
         with KernelTimes() as kt:
             entries = [StepEntry(r, [toks[state["i"]][j]], [0]) for j, r in enumerate(ids)]

@@ -41,11 +41,14 @@ __device__ __forceinline__ bf16* ftile(bf16* base, int pitch_chunks, int row, in
   return base + ((size_t)row * pitch_chunks + (chunk ^ (row & 7))) * 8;
 }
 
-template <int BLOCK_N, int DVB>
+// KSPLIT 4: items of at most 16 rows; every warp takes rows 0..15 and a quarter of each tile's keys, and the four
+// partial results are merged through shared memory at the end.
+template <int BLOCK_N, int DVB, int KSPLIT>
 __global__ void __launch_bounds__(128)
 attn_flex_kernel(const FlexParams p) {
   constexpr int THREADS = 128;
-  constexpr int NT = BLOCK_N / 8;
+  constexpr int NT = BLOCK_N / 8 / KSPLIT;          // score n-tiles of a warp
+  constexpr int KEYS_W = BLOCK_N / KSPLIT;          // keys of a tile that a warp takes
   constexpr int DT = DVB / 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int kch = p.dk_pitch / 8;                       // 16-byte chunks of a key row in shared memory
@@ -60,7 +63,9 @@ attn_flex_kernel(const FlexParams p) {
   const int item_idx = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
   const AttnItem item = p.items[item_idx];
   const int g = blockIdx.y / p.hparts, hpart = blockIdx.y % p.hparts;
-  const int wrow = p.warps_are_slices ? 0 : (threadIdx.x >> 5) * 16;          // first tile row of this warp
+  const int warp = threadIdx.x >> 5;
+  const int wrow = (p.warps_are_slices || KSPLIT > 1) ? 0 : warp * 16;        // first tile row of this warp
+  const int krow0 = KSPLIT > 1 ? warp * KEYS_W : 0;                           // first key row of a tile for this warp
   const int v0 = (p.warps_are_slices ? blockIdx.z * 4 + (threadIdx.x >> 5) : blockIdx.z) * DVB;   // first value column
   const int lane = threadIdx.x & 31;
   if (item.ntok <= 0) return;
@@ -175,8 +180,8 @@ attn_flex_kernel(const FlexParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();
-    bool skip = !warp_active || j0 > warp_max_pos;
-    if (p.window > 0 && j0 + BLOCK_N - 1 <= warp_min_pos - p.window) skip = true;
+    bool skip = !warp_active || j0 + krow0 > warp_max_pos;
+    if (p.window > 0 && j0 + krow0 + KEYS_W - 1 <= warp_min_pos - p.window) skip = true;
     if (!skip) {
       float s[NT][4];
 #pragma unroll
@@ -188,7 +193,7 @@ attn_flex_kernel(const FlexParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT; nt += 2) {
           unsigned b0, b1, b2, b3;
-          ldsm_x4(b0, b1, b2, b3, ftile(Kt, kch, nt * 8 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+          ldsm_x4(b0, b1, b2, b3, ftile(Kt, kch, krow0 + nt * 8 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
           mma_bf16(s[nt], a0, a1, a2, a3, b0, b1);
           mma_bf16(s[nt + 1], a0, a1, a2, a3, b2, b3);
         }
@@ -200,7 +205,7 @@ attn_flex_kernel(const FlexParams p) {
       for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const int j = j0 + krow0 + nt * 8 + (lane & 3) * 2 + (e & 1);
           const int pos = (e < 2) ? pos_lo : pos_hi;
           const bool vis = j >= kv_lo && j <= pos && (p.window <= 0 || j > pos - p.window);
           float v = -INFINITY;
@@ -240,7 +245,7 @@ attn_flex_kernel(const FlexParams p) {
       const int vch = own_v ? DT : kch;
       const int vc0 = own_v ? 0 : v0 / 8;
 #pragma unroll
-      for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+      for (int kk = 0; kk < KEYS_W / 16; ++kk) {
         const unsigned a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
         const unsigned a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
         const unsigned a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
@@ -249,13 +254,54 @@ attn_flex_kernel(const FlexParams p) {
         for (int dt = 0; dt < DT; dt += 2) {
           if (v0 + dt * 8 >= p.dv) break;                 // columns beyond the values: nothing there to read
           unsigned b0, b1, b2, b3;
-          ldsm_x4_t(b0, b1, b2, b3, ftile(Vt, vch, kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), vc0 + dt + (lane >> 4)));
+          ldsm_x4_t(b0, b1, b2, b3, ftile(Vt, vch, krow0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), vc0 + dt + (lane >> 4)));
           mma_bf16(o[dt], a0, a1, a2, a3, b0, b1);
           mma_bf16(o[dt + 1], a0, a1, a2, a3, b2, b3);
         }
       }
     }
     __syncthreads();       // everyone is done with this stage before it is refilled
+  }
+  if (KSPLIT > 1) {
+    // The warps hold partial results for the same rows and columns, lane by lane: warps 1.. hand theirs to warp 0
+    // through shared memory (the tiles are done with), which weighs them by their maxima and goes on alone.
+    constexpr int W = DT * 4 + 4;
+    float* X = reinterpret_cast<float*>(smem_raw);
+    if (warp > 0) {
+      float* mine = X + (size_t)(warp - 1) * W * 32 + lane;
+#pragma unroll
+      for (int i = 0; i < DT; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mine[(i * 4 + e) * 32] = o[i][e];
+      mine[(DT * 4 + 0) * 32] = m_lo; mine[(DT * 4 + 1) * 32] = m_hi;
+      mine[(DT * 4 + 2) * 32] = l_lo; mine[(DT * 4 + 3) * 32] = l_hi;
+    }
+    __syncthreads();
+    if (warp > 0) return;
+    float M_lo = m_lo, M_hi = m_hi;
+#pragma unroll
+    for (int w = 0; w < KSPLIT - 1; ++w) {
+      M_lo = fmaxf(M_lo, X[((size_t)w * W + DT * 4 + 0) * 32 + lane]);
+      M_hi = fmaxf(M_hi, X[((size_t)w * W + DT * 4 + 1) * 32 + lane]);
+    }
+    const float b_lo = M_lo == -INFINITY ? 0.f : M_lo, b_hi = M_hi == -INFINITY ? 0.f : M_hi;
+    const float f_lo = exp2f(m_lo - b_lo), f_hi = exp2f(m_hi - b_hi);
+    l_lo *= f_lo; l_hi *= f_hi;
+#pragma unroll
+    for (int i = 0; i < DT; ++i) { o[i][0] *= f_lo; o[i][1] *= f_lo; o[i][2] *= f_hi; o[i][3] *= f_hi; }
+#pragma unroll
+    for (int w = 0; w < KSPLIT - 1; ++w) {
+      const float* theirs = X + (size_t)w * W * 32 + lane;
+      const float g_lo = exp2f(theirs[(DT * 4 + 0) * 32] - b_lo), g_hi = exp2f(theirs[(DT * 4 + 1) * 32] - b_hi);
+      l_lo = fmaf(theirs[(DT * 4 + 2) * 32], g_lo, l_lo);
+      l_hi = fmaf(theirs[(DT * 4 + 3) * 32], g_hi, l_hi);
+#pragma unroll
+      for (int i = 0; i < DT; ++i) {
+        o[i][0] = fmaf(theirs[(i * 4 + 0) * 32], g_lo, o[i][0]); o[i][1] = fmaf(theirs[(i * 4 + 1) * 32], g_lo, o[i][1]);
+        o[i][2] = fmaf(theirs[(i * 4 + 2) * 32], g_hi, o[i][2]); o[i][3] = fmaf(theirs[(i * 4 + 3) * 32], g_hi, o[i][3]);
+      }
+    }
+    m_lo = M_lo; m_hi = M_hi;
   }
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
@@ -333,8 +379,14 @@ __global__ void attn_flex_merge_kernel(const FlexParams p) {
   bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)head * p.dv;
   for (int d = threadIdx.x; d < p.dv; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < p.nsplit; ++s)
-      if (w[s] > 0.f) acc += p.part_o[((slab0 + s) * FLEX_M + r) * p.dv + d] * w[s];
+    for (int s0 = 0; s0 < p.nsplit; s0 += 8) {            // eight loads in flight; shares without keys hold nothing
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = (s0 + u < p.nsplit && w[s0 + u] > 0.f) ? p.part_o[((slab0 + s0 + u) * FLEX_M + r) * p.dv + d] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc = fmaf(v[u], s0 + u < p.nsplit ? w[s0 + u] : 0.f, acc);
+    }
     dst[d] = __float2bfloat16_rn(acc * s_inv);
   }
 }
@@ -358,15 +410,17 @@ SI_EXPORT long long si_attn_flex_scratch_floats(int num_items, int H, int KV, in
   return (long long)num_items * gy * nsplit * FLEX_M * (dv + 2);
 }
 
-template <int BLOCK_N, int DVB>
+template <int BLOCK_N, int DVB, int KSPLIT>
 static int flex_launch(const FlexParams& p, int dslices, size_t smem, cudaStream_t stream) {
   static size_t configured = 0;
+  if (KSPLIT > 1 && smem < (size_t)(KSPLIT - 1) * 32 * (DVB / 2 + 4) * sizeof(float))
+    smem = (size_t)(KSPLIT - 1) * 32 * (DVB / 2 + 4) * sizeof(float);          // room for the warps' merge
   if (smem > 48 * 1024 && smem > configured) {
-    if (cudaFuncSetAttribute(attn_flex_kernel<BLOCK_N, DVB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_flex_kernel<BLOCK_N, DVB, KSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return -2;
     configured = smem;
   }
-  attn_flex_kernel<BLOCK_N, DVB><<<dim3(p.num_items * p.nsplit, p.KV * p.hparts, dslices), 128, smem, stream>>>(p);
+  attn_flex_kernel<BLOCK_N, DVB, KSPLIT><<<dim3(p.num_items * p.nsplit, p.KV * p.hparts, dslices), 128, smem, stream>>>(p);
   return 0;
 }
 
@@ -405,8 +459,11 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
   p.bias_in_smem = dist_bias && smem + bias_bytes <= 227 * 1024 ? 1 : 0;       // else each score fetches its own
   if (p.bias_in_smem) smem += bias_bytes;
   int rc;
-  if (block_n == 64) rc = dvb == 128 ? flex_launch<64, 128>(p, zblocks, smem, stream) : flex_launch<64, 64>(p, zblocks, smem, stream);
-  else rc = dvb == 128 ? flex_launch<32, 128>(p, zblocks, smem, stream) : flex_launch<32, 64>(p, zblocks, smem, stream);
+  // items of at most 16 rows otherwise: the four warps take a quarter of each tile's keys (tiles of 64 keys only)
+  const bool ksplit = !p.warps_are_slices && block_n == 64 && max_rows > 0 && max_rows <= 16;
+  if (ksplit) rc = dvb == 128 ? flex_launch<64, 128, 4>(p, zblocks, smem, stream) : flex_launch<64, 64, 4>(p, zblocks, smem, stream);
+  else if (block_n == 64) rc = dvb == 128 ? flex_launch<64, 128, 1>(p, zblocks, smem, stream) : flex_launch<64, 64, 1>(p, zblocks, smem, stream);
+  else rc = dvb == 128 ? flex_launch<32, 128, 1>(p, zblocks, smem, stream) : flex_launch<32, 64, 1>(p, zblocks, smem, stream);
   if (rc) return rc;
   if (nsplit > 1) {
     attn_flex_merge_kernel<<<dim3(num_items, KV * p.hparts, FLEX_M), 128, 0, stream>>>(p);

@@ -123,6 +123,10 @@ SI_EXPORT int si_causal_conv(const void* u, int dtype, long long u_stride, const
 // chunk after the one being computed is on its way into the other half of shared memory meanwhile (cp.async for B,
 // C and x; step size and decay by the first threads).
 #define SCAN_CHUNK 32
+#ifndef SCAN_UNROLL
+#define SCAN_UNROLL 8        // tokens whose loads the compiler may issue ahead of the sums of the token before
+#endif
+constexpr int kScanUnroll = SCAN_UNROLL;
 
 __device__ __forceinline__ void scan_cp16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
@@ -228,6 +232,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
     const float* hC = hB + SCAN_CHUNK * Npad;
     const float* hX = hC + SCAN_CHUNK * Npad;
     const float* hDec = hX + SCAN_CHUNK * Pbp;
+#pragma unroll kScanUnroll
     for (int r = 0; r < cn; ++r) {
       const float dec = hDec[r];
       const float xr = hX[r * Pbp + p - p0];

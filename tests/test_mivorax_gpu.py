@@ -232,7 +232,7 @@ def test_attention_kernels_far_keys_and_edges(case, kernel, dtype):
         again = torch.zeros_like(out)
         scratch = torch.zeros(ops.attn_flex_scratch_floats(ones.shape[0], H, KV, dv, 5), dtype=torch.float32, device=dev)
         ops.attn_flex(qd, kc.to(dev), vc, table.to(dev), ones, again, ps, 1, H, KV, dk, dv, b["scale"], 0, dist_bias=bias, sink=sink,
-                      nsplit=5, scratch=scratch)
+                      nsplit=5, scratch=scratch, max_rows=H // KV)
         diff = (again[600:].double().cpu().view(-1, H, dv) - b["ref"][600:]).abs().max().item()
         assert diff <= limit, f"{case}: rows in shares differ by {diff:.2e}"
     diff = (out.double().cpu().view(n, H, dv) - b["ref"]).abs().max().item()
