@@ -274,7 +274,7 @@ def mivorax_section(args) -> int:
     for name, cfg_d in (("mivorax", _mivorax_config()), ("llama", _llama_twin())):
         model = Model(config_from_dict(cfg_d), torch.bfloat16, "cuda:0")
         init_random(model, seed=0)
-        runner = ModelRunner(model, page_size=PAGE, num_pages=(B * CTX + PT) // PAGE + 8, max_requests=max(B, 2),
+        runner = ModelRunner(model, page_size=PAGE, num_pages=(B * CTX + PT) // PAGE + 8, max_requests=max(B, 2) + 1,
                              max_step_tokens=PT + B, max_seq_len=CTX)
         mgr = runner.manager
         for t in runner.storage.keys + runner.storage.values:
