@@ -65,9 +65,17 @@ MIXED_B = _model(500, 256, 2e-6, (509, 3, 1000003), [
     _layer("mamba2", _ssm(8, 32, 64, 2, 4, 2), ff=None, weights_of=2),
     _layer("attention", _attn(4, 1, 48, 80, 64.0, 8), ff=128),
 ])
-CONFIGS = {"attention": ONLY_ATTENTION, "latent": ONLY_LATENT, "ssm": ONLY_SSM, "pair_mlp": ONLY_PAIR_MLP,
+# sizes that are multiples of nothing useful: every kernel's general route (no 16-byte rows, no tensor-core tiles)
+ODD = _model(97, 70, 3e-5, (89, 5, 3), [
+    _layer("latent_attention", _latent(3, 12, 10, 14, 26, 36, base=77.0, dims=6), ff=50),
+    _layer("mamba2", _ssm(6, 5, 10, 3, 3, 2), ff=None),
+    _layer("attention", _attn(5, 5, 20, 12, 33.0, 14), ff=46),
+    _layer("mamba2", _ssm(2, 9, 7, 1, 5, 3), ff=18),
+    _layer("attention", _attn(6, 2, 7, 9, 21.5, 6), ff=None),
+])
+CONFIGS = {"odd": ODD, "attention": ONLY_ATTENTION, "latent": ONLY_LATENT, "ssm": ONLY_SSM, "pair_mlp": ONLY_PAIR_MLP,
            "mixed_a": MIXED_A, "mixed_b": MIXED_B}
-PAGE_SIZE = {"attention": 8, "latent": 16, "ssm": 16, "pair_mlp": 4, "mixed_a": 8, "mixed_b": 16}
+PAGE_SIZE = {"odd": 4, "attention": 8, "latent": 16, "ssm": 16, "pair_mlp": 4, "mixed_a": 8, "mixed_b": 16}
 
 
 def _tensors(cfg, seed):

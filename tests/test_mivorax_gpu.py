@@ -97,7 +97,7 @@ def test_layers_one_by_one_in_32_bit(folders, name):
 # ---- schedules ------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("name", ["mixed_a", "mixed_b"])
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_schedules(folders, plains, name, dtype, mode):
     reqs = requests_of(name, [1, 3, 19, 64, 65, 130, 201], seed=1)
@@ -336,7 +336,7 @@ def test_state_space_kernels_in_portions(heads, P, N, groups, taps):
 
 # ---- the entry point ----------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("name", ["mixed_a", "mixed_b"])
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
 def test_greedy_generation_through_the_entry_point(folders, name):
     """Greedy tokens through LLM (scheduler, sampler, graphs and steps launched ahead where the model allows) equal the
     plain implementation's in 32-bit; bfloat16 runs and mostly agrees."""
