@@ -232,6 +232,45 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
     const float* hC = hB + SCAN_CHUNK * Npad;
     const float* hX = hC + SCAN_CHUNK * Npad;
     const float* hDec = hX + SCAN_CHUNK * Pbp;
+    if (NS == 8) {
+      // Eight lanes a column: the lanes' partial sums of eight tokens are added up together by exchanging halves
+      // (4 + 2 + 1 shuffles for eight tokens, and off the per-token chain), lane ns ending with token ns of the eight.
+      for (int r0 = 0; r0 < cn; r0 += 8) {
+        float acc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc[u] = 0.f;
+          if (r0 + u < cn) {
+            const int r = r0 + u;
+            const float dec = hDec[r];
+            const float dx = hX[r * Pbp + p - p0] * hDec[SCAN_CHUNK + r];
+            const float4* Br = reinterpret_cast<const float4*>(hB + r * Npad) + ns;
+            const float4* Cr = reinterpret_cast<const float4*>(hC + r * Npad) + ns;
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int i4 = 0; i4 < NPT / 4; ++i4) {
+              const float4 b = Br[i4 * 8], c = Cr[i4 * 8];
+              S[4 * i4 + 0] = fmaf(dec, S[4 * i4 + 0], dx * b.x); a0 = fmaf(S[4 * i4 + 0], c.x, a0);
+              S[4 * i4 + 1] = fmaf(dec, S[4 * i4 + 1], dx * b.y); a1 = fmaf(S[4 * i4 + 1], c.y, a1);
+              S[4 * i4 + 2] = fmaf(dec, S[4 * i4 + 2], dx * b.z); a0 = fmaf(S[4 * i4 + 2], c.z, a0);
+              S[4 * i4 + 3] = fmaf(dec, S[4 * i4 + 3], dx * b.w); a1 = fmaf(S[4 * i4 + 3], c.w, a1);
+            }
+            acc[u] = a0 + a1;
+          }
+        }
+        const bool b4 = ns & 4, b2 = ns & 2, b1 = ns & 1;
+        float h4[4], h2[2];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          h4[u] = (b4 ? acc[4 + u] : acc[u]) + __shfl_xor_sync(0xffffffffu, b4 ? acc[u] : acc[4 + u], 4);
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          h2[u] = (b2 ? h4[2 + u] : h4[u]) + __shfl_xor_sync(0xffffffffu, b2 ? h4[u] : h4[2 + u], 2);
+        const float v = (b1 ? h2[1] : h2[0]) + __shfl_xor_sync(0xffffffffu, b1 ? h2[0] : h2[1], 1);
+        const int r = r0 + ns;
+        if (r < cn && live) y[(size_t)(row0 + c0 + r) * y_stride + (size_t)h * P + p] = v + dskip * hX[r * Pbp + p - p0];
+      }
+    } else {
 #pragma unroll kScanUnroll
     for (int r = 0; r < cn; ++r) {
       const float dec = hDec[r];
@@ -252,6 +291,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_str
       for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, NS);
       if (ns == 0 && live) y[(size_t)(row0 + c0 + r) * y_stride + (size_t)h * P + p] = acc + dskip * xr;
     }
+    }
     __syncthreads();       // everyone is done with this half before it is filled again
   }
   if (live) {
@@ -268,15 +308,10 @@ static int scan_launch(const float* xbc, long long xbc_stride, const void* dt_ra
   // Cut the columns over more blocks while the blocks still find a multiprocessor each, down to 8 columns a block:
   // a block's time goes to reading B and C from shared memory once per column, so columns on idle multiprocessors
   // are time saved; beyond one block each, the cut only repeats the staging of B and C (measured at 64 heads, one
-  // sequence of 2,048 rows: 64 blocks 1.37 ms, 512 blocks of 8 columns 4.26 ms). The state's layout does not
-  // depend on the cut.
+  // sequence of 2,048 rows: 128 blocks 0.63 ms, 256 blocks 0.74 ms, 512 blocks of 8 columns 1.35 ms). The state's
+  // layout does not depend on the cut.
   int Pb = P;
-  static int per_sm = 0;
-  if (per_sm == 0) {
-    const char* e = getenv("SI_SCAN_BLOCKS_PER_SM");
-    per_sm = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 1;
-  }
-  while (Pb % 2 == 0 && Pb / 2 >= 8 && 2LL * num_seqs * heads * (P / Pb) <= (long long)per_sm * si_sm_count()) Pb /= 2;
+  while (Pb % 2 == 0 && Pb / 2 >= 8 && 2LL * num_seqs * heads * (P / Pb) <= si_sm_count()) Pb /= 2;
   int threads = (Pb * NS + 31) / 32 * 32;
   const size_t smem = (size_t)2 * (2 * SCAN_CHUNK * NS * NPT + SCAN_CHUNK * ((Pb + 3) / 4 * 4) + 2 * SCAN_CHUNK) * sizeof(float);
   if (smem > 200 * 1024) return -2;
