@@ -1,4 +1,5 @@
-"""A small, whole, single-GPU inference engine for the Llama 3 dense architecture on B200:
+"""A small, whole, single-GPU inference engine on B200 for the Llama 3 dense architecture and for Mivorax (layers
+listed one by one: attention with a distance bias, latent attention, state-space mixers):
 typed configuration and architecture registry, weights by tensor name, layers put together
 from parts, a paged cache manager, one step function for mixed batches, a scheduler,
 sampling, and hand-written sm_100a kernels with a bfloat16 and a true float32 path.
