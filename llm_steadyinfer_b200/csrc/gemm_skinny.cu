@@ -37,6 +37,8 @@ struct SkinnyRope {
   bf16* v_cache;
   int table_width, num_pages, page_size, num_seqs, H, KV, hs;
   int* status;
+  int act;                   // plain store only: 1 = the square of relu of the sum (rounded to bf16 first, as a stored
+                             // product followed by the activation kernel gives); 0 = the sum as it is
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -220,6 +222,10 @@ gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __rest
       for (int w = 0; w < WARPS; ++w) s += red[w][mt][ln][e];
       const int n = n0 + (ln >> 2) + ((e >> 1) ? 8 : 0);
       const int m = mt * 8 + (ln & 3) * 2 + (e & 1);
+      if (rope.act == 1) {
+        s = fmaxf(__bfloat162float(__float2bfloat16_rn(s)), 0.f);
+        s *= s;
+      }
       if (n < N && m < M) store_out<TO>(out + (size_t)m * ldo + n, s);
     }
   }
@@ -266,6 +272,18 @@ SI_EXPORT int si_gemm_skinny(const void* x, long long ldx, const void* W, long l
   return si_last_error();
 }
 
+// out[M, N] (bf16) = relu(x W^T)^2, the activation in the product's epilogue.
+SI_EXPORT int si_gemm_skinny_relu2(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
+                                   int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return -2;
+  if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
+  SkinnyRope r = SkinnyRope();
+  r.act = 1;
+  skinny_dispatch<bf16, false, false>((unsigned)((N + 15) / 16), stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K, r);
+  return si_last_error();
+}
+
 // out[M, F] = silu(gate) * up of the stacked projection x[M, K] W[2F, K]^T whose rows are interleaved in
 // groups of 8 (8 gates, their 8 ups, ...); F a multiple of 8, bf16 output.
 SI_EXPORT int si_gemm_skinny_swiglu(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
@@ -293,7 +311,7 @@ SI_EXPORT int si_gemm_skinny_qkv_rope(const void* x, long long ldx, const void* 
   if (k_cache && (!v_cache || !block_table)) return -2;
   const int N = (H + 2 * KV) * hs;
   const unsigned blocks = (unsigned)((H + 2 * KV) * (hs / 16));
-  SkinnyRope r;
+  SkinnyRope r = SkinnyRope();
   r.positions = positions; r.row_seq = row_seq; r.inv_freq = inv_freq; r.block_table = block_table;
   r.k_cache = (bf16*)k_cache; r.v_cache = (bf16*)v_cache;
   r.table_width = table_width; r.num_pages = num_pages; r.page_size = page_size; r.num_seqs = num_seqs;

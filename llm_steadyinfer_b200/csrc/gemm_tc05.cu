@@ -67,7 +67,17 @@ __device__ __forceinline__ void add_row32(float* dst, const float (&v)[32], int 
 }
 
 // What the epilogue does with a tile: store it, store silu(gate) * up of it, or add it into an fp32 tensor.
-enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2 };
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2, EPI_RELU2 = 3 };
+
+// The square of relu of every sum, each rounded to bf16 first (what a stored product followed by the activation
+// kernel gives).
+__device__ __forceinline__ void relu2_row32(float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float r = fmaxf(__bfloat162float(__float2bfloat16_rn(v[i])), 0.f);
+    v[i] = r * r;
+  }
+}
 
 // 16 outputs of the gated activation from 32 accumulator columns (two groups of 8 gates + 8 ups); gate and
 // up are rounded to bf16 first, as when the projection is stored and a second kernel applies the activation.
@@ -208,7 +218,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
           if (row < M && n < N) {
             if (EPI == EPI_SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
             else if (EPI == EPI_ADD) add_row32((float*)out + (size_t)row * ldo + n, v[c], min(32, N - n), vec4);
-            else store_row32<TO>(out + (size_t)row * ldo + n, v[c], min(32, N - n), vec);
+            else {
+              if (EPI == EPI_RELU2) relu2_row32(v[c]);
+              store_row32<TO>(out + (size_t)row * ldo + n, v[c], min(32, N - n), vec);
+            }
           }
         }
       }
@@ -362,7 +375,10 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
           if (row < M && n < N) {
             if (EPI == EPI_SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
             else if (EPI == EPI_ADD) add_row32((float*)out + (size_t)row * ldo + n, v[c], min(32, N - n), vec4);
-            else store_row32<TO>(out + (size_t)row * ldo + n, v[c], min(32, N - n), vec);
+            else {
+              if (EPI == EPI_RELU2) relu2_row32(v[c]);
+              store_row32<TO>(out + (size_t)row * ldo + n, v[c], min(32, N - n), vec);
+            }
           }
         }
       }
@@ -460,6 +476,17 @@ SI_EXPORT int si_gemm_tc05_swiglu(const void* x, long long ldx, const void* wmap
   if (use_pair(M, wmap_half)) return launch_pair<bf16, EPI_SWIGLU>(am, *(const CUtensorMap*)wmap_half, out, ldo, M, 2 * F, K, status, stream);
   const CUtensorMap& bm = *(const CUtensorMap*)wmap;
   return launch<4, bf16, EPI_SWIGLU>(am, bm, out, ldo, M, 2 * F, K, status, stream);
+}
+
+// out[M, N] (bf16) = relu(x W^T)^2: a feed-forward's activation in the epilogue of its first product.
+SI_EXPORT int si_gemm_tc05_relu2(const void* x, long long ldx, const void* wmap, const void* wmap_half, void* out,
+                                 long long ldo, int M, int N, int K, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  CUtensorMap am;
+  const int rc = gemm_tc05_common(x, ldx, wmap, &am, M, K);
+  if (rc) return rc;
+  if (use_pair(M, wmap_half)) return launch_pair<bf16, EPI_RELU2>(am, *(const CUtensorMap*)wmap_half, out, ldo, M, N, K, status, stream);
+  return launch<4, bf16, EPI_RELU2>(am, *(const CUtensorMap*)wmap, out, ldo, M, N, K, status, stream);
 }
 
 // resid[M, N] (fp32, rows `ldr` apart) += x[M, K] W[N, K]^T, each sum rounded to bf16 before it is added: the

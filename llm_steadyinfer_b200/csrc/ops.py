@@ -601,6 +601,18 @@ def gemm_skinny(a, w, out, checked: bool = False) -> None:
            f"gemm_skinny(M={M}, N={N}, K={K})")
 
 
+def gemm_skinny_relu2(a, w, out, checked: bool = False) -> None:
+    """out[M,N] (bf16) = relu(a[M,K] @ w[N,K]^T)^2 for M <= 16: the activation runs in the product's epilogue."""
+    _cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N) and out.dtype == torch.bfloat16, "gemm_skinny_relu2: shapes, bf16 output")
+    _need(checked or gemm_skinny_ok(a, w, out), "gemm_skinny_relu2: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_skinny", "si_gemm_skinny_relu2", [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()),
+           f"gemm_skinny_relu2(M={M}, N={N}, K={K})")
+
+
 def gemm_skinny_swiglu(a, w, out, checked: bool = False) -> None:
     """out[M,F] = silu(gate) * up of a[M,K] @ w[2F,K]^T for M <= 16, the rows of w interleaved in groups of 8
     (8 gates, their 8 ups, ...): the activation runs in the product's epilogue."""
@@ -714,6 +726,19 @@ def gemm_tc05_add(a, w, resid, status=None) -> None:
     half = _weight_map(w, 128) if M > 128 else None
     _check(f(_ptr(a), a.stride(0), _weight_map(w), half, _ptr(resid), resid.stride(0), M, N, K, _ptr(status), _stream()),
            f"gemm_tc05_add(M={M}, N={N}, K={K})")
+
+
+def gemm_tc05_relu2(a, w, out, status=None) -> None:
+    """out[M,N] (bf16) = relu(a[M,K] @ w[N,K]^T)^2 on the tcgen05 tensor cores, the activation in the epilogue."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N) and out.dtype == torch.bfloat16, "gemm_tc05_relu2: shapes, bf16 output")
+    _need(gemm_tc05_ok(a, w, out), "gemm_tc05_relu2: bf16 inputs, K a multiple of 8, 16-byte aligned rows")
+    f = _fn("gemm_tc05", "si_gemm_tc05_relu2", [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_p])
+    half = _weight_map(w, 128) if M > 128 else None
+    _check(f(_ptr(a), a.stride(0), _weight_map(w), half, _ptr(out), out.stride(0), M, N, K, _ptr(status), _stream()),
+           f"gemm_tc05_relu2(M={M}, N={N}, K={K})")
 
 
 def gemm_tc05_swiglu(a, w, out, status=None) -> None:

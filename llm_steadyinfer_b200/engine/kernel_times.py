@@ -30,7 +30,7 @@ KINDS = {
     "gemm_rows": "gemm_rows", "gemm_rows_swiglu": "gemm_rows_swiglu",
     "embedding_pair": "embedding", "rmsnorm_rows": "rmsnorm_rows", "attention_general": "attention_general",
     "attn_flex": "attn_flex", "kv_store": "kv_store", "latent_prepare": "latent_prepare", "activation": "activation",
-    "gemm_heads": "gemm_heads", "latent_gather": "latent_gather", "latent_expand_keys": "latent_expand_keys", "causal_conv": "causal_conv", "ssm_scan": "ssm_scan", "gated_part_norm": "gated_part_norm",
+    "gemm_heads": "gemm_heads", "gemm_skinny_relu2": "gemm_skinny_relu2", "gemm_tc05_relu2": "gemm_tc05_relu2", "latent_gather": "latent_gather", "latent_expand_keys": "latent_expand_keys", "causal_conv": "causal_conv", "ssm_scan": "ssm_scan", "gated_part_norm": "gated_part_norm",
 }
 
 

@@ -116,8 +116,15 @@ class DenseMLP(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         act = ctx.buf("ffn_act", (T, self.inter), self.dtype)
-        linear(x, self.up, act, ctx.status)
-        ops.activation(act, act, self.activation)
+        fused = self.activation == "relu2" and act.dtype == torch.bfloat16
+        if fused and linear_mod.USE_SKINNY and ops.gemm_skinny_ok(x, self.up, act):
+            ops.gemm_skinny_relu2(x, self.up, act, checked=True)              # decode rows: activation in the epilogue
+        elif (fused and linear_mod.USE_OWN_GEMM and T >= linear_mod.OWN_GEMM_MIN_ROWS and ops.gemm_tc05_available()
+                and ops.gemm_tc05_ok(x, self.up, act)):
+            ops.gemm_tc05_relu2(x, self.up, act, ctx.status)                  # prompt portions: likewise, on tcgen05
+        else:
+            linear(x, self.up, act, ctx.status)
+            ops.activation(act, act, self.activation)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(act, self.down, out, ctx.status)
         return out

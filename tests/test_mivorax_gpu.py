@@ -434,3 +434,25 @@ def test_command_line_serves_the_design(folders, tmp_path):
         assert proc.returncode == 0, proc.stderr[-3000:]
         m = json.loads(out.read_text())[0]
         assert m["completed"] == 12 and m["rejected"] == 0 and m["output_tokens"] > 12 and m["output_tps"] > 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 5632, 2048), (16, 40, 72), (128, 384, 256), (300, 1000, 136), (2048, 520, 256)])
+def test_products_with_the_activation_in_the_epilogue(M, N, K):
+    """relu(x W^T)^2 from the few-row product and from the tcgen05 product against the product stored in bfloat16 and
+    the activation kernel after it."""
+    from llm_steadyinfer_b200.csrc import ops
+    from llm_steadyinfer_b200.parts.linear import linear
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda:0").bfloat16()
+    w = (torch.randn(N, K, device="cuda:0") / K ** 0.5).bfloat16()
+    want = torch.empty(M, N, device="cuda:0", dtype=torch.bfloat16)
+    linear(x, w, want)
+    ops.activation(want, want, "relu2")
+    got = torch.full_like(want, 3.0)
+    if M <= 16:
+        ops.gemm_skinny_relu2(x, w, got)
+    else:
+        ops.gemm_tc05_relu2(x, w, got)
+    ref = torch.relu(x.float() @ w.float().T) ** 2
+    assert (got.float() - ref).abs().max().item() <= 0.05 * max(1.0, ref.abs().max().item())
+    assert (got.float() - want.float()).abs().max().item() <= 0.02 * max(1.0, ref.abs().max().item())
