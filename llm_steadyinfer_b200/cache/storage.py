@@ -1,6 +1,6 @@
 """Device tensors behind the cache manager: per group one key and one value tensor
-``[layers_in_group, num_pages, kv_heads, page_size, head_dim]`` (values with their own last size, or none at all
-for a group whose keys serve as values) and, for mixers with fixed-size state, one tensor ``[slots, *shape]`` per
+``[layers_in_group, num_pages, kv_heads, page_size, head_dim]`` (values with their own last size and head count, or
+none at all for a group whose keys serve as values) and, for mixers with fixed-size state, one tensor ``[slots, *shape]`` per
 layer; a place of the layout without a mixer (the embedder's, last) has its state here as well. The reference keeps
 ``[L, num_blocks, block_size, kv_dim]`` in fp32 (src/source/scheduler/kv_manager.cpp:41-53);
 here a page holds each head's rows contiguously and has the compute dtype.
@@ -40,8 +40,8 @@ class CacheStorage:
             shape = (len(grp.layers), grp.pool.num_pages, grp.need.num_kv_heads, ps)
             self.keys.append(torch.zeros(shape + (grp.need.head_dim,), dtype=dtype, device=self.device))
             # a group without values of their own (value_dim 0) has no second tensor
-            self.values.append(torch.zeros(shape + (grp.need.v_dim,), dtype=dtype, device=self.device)
-                               if grp.need.v_dim else None)
+            vshape = (len(grp.layers), grp.pool.num_pages, grp.need.v_heads, ps, grp.need.v_dim)
+            self.values.append(torch.zeros(vshape, dtype=dtype, device=self.device) if grp.need.v_dim else None)
         self.states: List[Optional[torch.Tensor]] = []
         for s in layout.states:
             self.states.append(None if s is None else torch.zeros(

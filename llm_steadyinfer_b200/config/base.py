@@ -61,6 +61,10 @@ class EmbedderSpec:
 class LayerSpec:
     """One block: ``h += mixer(norm(h)); h += ffn(norm(h))`` for arrangement "pre_norm".
 
+    With arrangement "sandwich" each sublayer has a second norm behind it, applied to the sublayer's result before
+    it joins the stream (``mixer_post_norm``, ``feed_forward_post_norm``):
+    ``h += norm_b(mixer(norm(h))); h += norm_b(ffn(norm(h)))``.
+
     ``weight_prefix`` is the checkpoint prefix of this layer ("model.layers.3.").
     ``cache_from`` is None when the layer owns its cache, or the index of the layer
     whose cache it reads (it then writes nothing): that of the latest run of that layer
@@ -78,6 +82,23 @@ class LayerSpec:
     feed_forward_prefix: str = "mlp."
     mixer_norm_name: str = "input_layernorm."
     feed_forward_norm_name: str = "post_attention_layernorm."
+    # norms behind the sublayers (arrangement "sandwich")
+    mixer_post_norm: Optional[NormSpec] = None
+    feed_forward_post_norm: Optional[NormSpec] = None
+    mixer_post_norm_name: str = "post_mixer_norm."
+    feed_forward_post_norm_name: str = "post_feed_forward_norm."
+
+
+@dataclass(frozen=True)
+class StreamAddSpec:
+    """Something the residual stream gains between layers: before the run at ``place`` of the run order, the
+    embedder's output (the stream as it was before the first layer) is added again if ``embedding`` is set, and row
+    ``row`` of the checkpoint tensor ``vector_name`` ([rows, hidden]) if a name is given. Models that run a span
+    of layers several times use it at the start of each pass."""
+    place: int
+    embedding: bool = False
+    vector_name: Optional[str] = None
+    row: int = 0
 
 
 @dataclass(frozen=True)
@@ -93,6 +114,9 @@ class ModelSpec:
     lm_head_name: str = "lm_head.weight"
     max_position: int = 0
     embedder: Optional[EmbedderSpec] = None      # None: the plain table under ``embed_name``
+    stream_adds: tuple = ()                      # StreamAddSpec entries, at most one a place
+    stream_vector_shapes: Optional[Dict[str, tuple]] = None   # the tensors that ``stream_adds`` name: name -> shape
+    logit_softcap: float = 0.0                   # > 0: logits <- cap * tanh(logits / cap)
 
 
 class ModelConfig:

@@ -4,7 +4,11 @@
 //   * a key size dk and a value size dv that differ,
 //   * values that are the first dv entries of the keys (v_cache == nullptr: a latent that serves as both),
 //   * a bias by distance: bias[min(i - j, nd - 1), head] (fp32 table [nd, H]) added to the scaled score,
-//   * a sink per head: exp(sink[h]) joins the softmax denominator once, with no key and no value.
+//   * a sink per head: exp(sink[h]) joins the softmax denominator once, with no key and no value,
+//   * a soft limit on the scaled score: s <- softcap * tanh(s / softcap) (before the bias),
+//   * key heads that share a value head: `v_share` neighbouring key heads read one value head (the cache then holds
+//     KV / v_share value heads), as the maps of a differential attention do,
+//   * results in fp32 whatever the storage (out_f32), for a caller that goes on subtracting them.
 //     s_j = scale * q_h . K[j, g] + bias[min(pos - j, nd - 1), h],  j in [max(0, pos - window + 1), pos]
 //     out_h = sum_j exp(s_j) V[j, g] / (sum_j exp(s_j) + exp(sink_h))
 // One block per (token row, query head); warp w of 4 walks keys j0 + w, j0 + w + 4, ... with a running
@@ -18,26 +22,26 @@
 #define GEN_WARPS 4
 #define GEN_MAX_PER_LANE 20   // key and value sizes up to 640
 
-template <typename T>
+template <typename T, typename TO>
 __global__ void __launch_bounds__(GEN_WARPS * 32)
 attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
                          const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                          const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ row_seq, const int* __restrict__ positions,
-                         T* __restrict__ out, long long out_row_stride, int num_pages,
+                         TO* __restrict__ out, long long out_row_stride, int num_pages,
                          int page_size, int num_seqs, int H, int KV, int dk, int dv, float scale,
                          int window, const float* __restrict__ dist_bias, int nd,
-                         const float* __restrict__ sink, int* status) {
+                         const float* __restrict__ sink, float softcap, int v_share, int* status) {
   extern __shared__ float smem[];   // [GEN_WARPS][dv] accumulators, then m[GEN_WARPS], l[GEN_WARPS]
   const int t = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = h / (H / KV);
   const int pos = positions[t];
   const int seq = row_seq[t];
-  T* o = out + (size_t)t * out_row_stride + (size_t)h * dv;
+  TO* o = out + (size_t)t * out_row_stride + (size_t)h * dv;
   if (seq < 0 || seq >= num_seqs) {      // seq < 0 marks a padding row of a fixed-shape step
     if (threadIdx.x == 0 && seq >= 0) set_status(status, SI_BAD_SEQ);
-    for (int d = threadIdx.x; d < dv; d += blockDim.x) o[d] = from_f32<T>(0.f);
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) o[d] = from_f32<TO>(0.f);
     return;
   }
   const int* table = block_table + (size_t)seq * table_width;
@@ -63,7 +67,8 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
     }
     const size_t tok = ((size_t)page * KV + g) * page_size + (j - slot * page_size);
     const T* kp = k_cache + tok * dk;
-    const T* vp = vbase + tok * v_stride;
+    const T* vp = vbase + (v_share > 1 ? ((size_t)page * (KV / v_share) + g / v_share) * page_size + (j - slot * page_size)
+                                       : tok) * v_stride;
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
@@ -71,6 +76,7 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
       if (d < dk) dot += qr[i] * to_f32<T>(kp[d]);
     }
     dot = warp_sum(dot) * scale;
+    if (softcap > 0.f) dot = softcap * tanhf(dot / softcap);
     if (dist_bias) dot += dist_bias[(size_t)min(pos - j, nd - 1) * H + h];
     const float m_new = fmaxf(m, dot);
     const float corr = expf(m - m_new);
@@ -106,7 +112,7 @@ attention_general_kernel(const T* __restrict__ q, long long q_row_stride,
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < GEN_WARPS; ++w) v += sacc[w * dv + d] * wgt[w];
-    o[d] = from_f32<T>(L > 0.f ? v / L : 0.f);
+    o[d] = from_f32<TO>(L > 0.f ? v / L : 0.f);
   }
 }
 
@@ -115,24 +121,30 @@ SI_EXPORT int si_attention_general(const void* q, int dtype, long long q_row_str
                                    const int* row_seq, const int* positions, void* out,
                                    long long out_row_stride, int num_pages, int page_size, int num_tokens,
                                    int num_seqs, int H, int KV, int dk, int dv, float scale, int window,
-                                   const float* dist_bias, int nd, const float* sink, int* status,
-                                   cudaStream_t stream) {
+                                   const float* dist_bias, int nd, const float* sink, float softcap, int v_share,
+                                   int out_f32, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (dk > 32 * GEN_MAX_PER_LANE || dv > 32 * GEN_MAX_PER_LANE || dk <= 0 || dv <= 0 || KV <= 0 || H % KV) return -2;
   if (!v_cache && dv > dk) return -2;
+  if (v_share < 1 || KV % v_share || (v_share > 1 && !v_cache)) return -2;
   if (dist_bias && nd <= 0) return -2;
   dim3 grid(num_tokens, H);
   const size_t smem = (size_t)(GEN_WARPS * dv + 2 * GEN_WARPS) * sizeof(float);
-  if (dtype == SI_BF16)
-    attention_general_kernel<__nv_bfloat16><<<grid, GEN_WARPS * 32, smem, stream>>>(
+  if (dtype == SI_BF16 && out_f32)
+    attention_general_kernel<__nv_bfloat16, float><<<grid, GEN_WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+        block_table, table_width, row_seq, positions, (float*)out, out_row_stride, num_pages,
+        page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
+  else if (dtype == SI_BF16)
+    attention_general_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, GEN_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         block_table, table_width, row_seq, positions, (__nv_bfloat16*)out, out_row_stride, num_pages,
-        page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, status);
+        page_size, num_seqs, H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
   else
-    attention_general_kernel<float><<<grid, GEN_WARPS * 32, smem, stream>>>(
+    attention_general_kernel<float, float><<<grid, GEN_WARPS * 32, smem, stream>>>(
         (const float*)q, q_row_stride, (const float*)k_cache, (const float*)v_cache, block_table,
         table_width, row_seq, positions, (float*)out, out_row_stride, num_pages, page_size, num_seqs,
-        H, KV, dk, dv, scale, window, dist_bias, nd, sink, status);
+        H, KV, dk, dv, scale, window, dist_bias, nd, sink, softcap, v_share, status);
   return si_last_error();
 }
 

@@ -1,5 +1,5 @@
-// Embedding gather: out[t, :] = table[tokens[t], :], widened to fp32 (the residual
-// stream is fp32 in both precisions). The reference's kernel
+// Embedding gather: out[t, :] = scale * table[tokens[t], :], widened to fp32 (the residual
+// stream is fp32 in both precisions; the product with the scale is fp32 too). The reference's kernel
 // (src/source/op/kernels/cuda/emb_kernel.cu:3-21) silently skips token ids outside
 // the vocabulary; here such a row is zeroed and the status word is set.
 #include "common.cuh"
@@ -7,7 +7,7 @@
 template <typename TW>
 __global__ void embedding_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab,
-                                        int* status) {
+                                        float scale, int* status) {
   pdl_prologue();
   const int t = blockIdx.x;
   const int tok = tokens[t];
@@ -18,20 +18,20 @@ __global__ void embedding_gather_kernel(const int* __restrict__ tokens, const TW
     return;
   }
   const TW* w = table + (size_t)tok * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<TW>(w[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = scale * to_f32<TW>(w[i]);
 }
 
 SI_EXPORT int si_embedding_gather(const int* tokens, const void* table, int table_dtype, float* out,
-                                  int num_tokens, int hidden, int vocab, int* status,
+                                  int num_tokens, int hidden, int vocab, float scale, int* status,
                                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == SI_BF16)
     si_launch(embedding_gather_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream,
-              tokens, (const __nv_bfloat16*)table, out, hidden, vocab, status);
+              tokens, (const __nv_bfloat16*)table, out, hidden, vocab, scale, status);
   else
     si_launch(embedding_gather_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
-              tokens, (const float*)table, out, hidden, vocab, status);
+              tokens, (const float*)table, out, hidden, vocab, scale, status);
   return si_last_error();
 }
 

@@ -231,3 +231,89 @@ SI_EXPORT int si_rmsnorm_rows(const void* x, void* out, int x_dtype, const void*
   return rows_launch<float, float>(x, out, weight, num_rows, n, inner, x_outer, x_inner, o_outer, o_inner, eps, stream);
 }
 
+
+// ---- the add in its general form --------------------------------------------------------------------------------
+// What blocks with a norm behind each sublayer, and models that feed something into the stream between layers, need:
+//   d  = delta (+ delta_bias)                                    the sublayer's result
+//   d' = delta_weight * d * rsqrt(mean(d^2) + delta_eps)         when delta_weight is given, else d' = d
+//   h  = resid + d' (+ extra[row]) (+ vec);   resid <- h  (not with `rows`)
+//   out = weight * h * rsqrt(mean(h^2) + eps)                    when out is given
+// delta, extra, vec, out may each be absent. All statistics and sums are fp32. One block a row; the row (and the
+// delta's) is staged in shared memory, so any width up to what shared memory holds.
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(256) add_norm_general_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
+    const float* __restrict__ delta_bias, const TW* __restrict__ delta_weight, float delta_eps,
+    const float* __restrict__ extra, const float* __restrict__ vec, const int* __restrict__ rows,
+    const TW* __restrict__ weight, TX* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  extern __shared__ float row_cache[];        // `hidden` floats
+  pdl_prologue();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* h = resid + (size_t)src * hidden;
+  float dscale = 1.f;
+  if (delta && delta_weight) {
+    const TX* dl = delta + (size_t)src * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = to_f32<TX>(dl[i]) + (delta_bias ? delta_bias[i] : 0.f);
+      ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    dscale = rsqrtf(ss / (float)hidden + delta_eps);
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = h[i];
+    if (delta) {
+      float d = to_f32<TX>(delta[(size_t)src * hidden + i]) + (delta_bias ? delta_bias[i] : 0.f);
+      if (delta_weight) d = to_f32<TW>(delta_weight[i]) * (d * dscale);
+      v += d;
+    }
+    if (extra) v += extra[(size_t)src * hidden + i];
+    if (vec) v += vec[i];
+    row_cache[i] = v;
+    if (!rows) h[i] = v;
+    ss += v * v;
+  }
+  if (!out) return;
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TX* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    o[i] = from_f32<TX>(to_f32<TW>(weight[i]) * (row_cache[i] * inv));
+}
+
+template <typename TX, typename TW>
+static int general_launch(float* resid, const void* delta, const float* delta_bias, const void* delta_weight, float delta_eps,
+                          const float* extra, const float* vec, const int* rows, const void* weight, void* out, int num_rows,
+                          int hidden, float eps, cudaStream_t stream) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  static size_t configured = 0;
+  auto k = add_norm_general_kernel<TX, TW>;
+  if (smem > 48 * 1024 && smem > configured) {
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -2;
+    configured = smem;
+  }
+  si_launch(k, dim3(num_rows), dim3(hidden >= 1024 ? 256 : 128), smem, stream, resid, (const TX*)delta, delta_bias,
+            (const TW*)delta_weight, delta_eps, extra, vec, rows, (const TW*)weight, (TX*)out, hidden, eps);
+  return si_last_error();
+}
+
+// x_dtype: dtype of delta and out; weight_dtype: dtype of weight and delta_weight. Returns 0, a CUDA error code, or -2.
+SI_EXPORT int si_add_norm_general(float* resid, const void* delta, const float* delta_bias, const void* delta_weight,
+                                  float delta_eps, const float* extra, const float* vec, const int* rows,
+                                  const void* weight, int weight_dtype, void* out, int x_dtype, int num_rows, int hidden,
+                                  float eps, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (out && !weight) return -2;
+  if (x_dtype == SI_BF16) {
+    if (weight_dtype == SI_BF16)
+      return general_launch<__nv_bfloat16, __nv_bfloat16>(resid, delta, delta_bias, delta_weight, delta_eps, extra, vec, rows, weight, out, num_rows, hidden, eps, stream);
+    return general_launch<__nv_bfloat16, float>(resid, delta, delta_bias, delta_weight, delta_eps, extra, vec, rows, weight, out, num_rows, hidden, eps, stream);
+  }
+  if (weight_dtype == SI_BF16)
+    return general_launch<float, __nv_bfloat16>(resid, delta, delta_bias, delta_weight, delta_eps, extra, vec, rows, weight, out, num_rows, hidden, eps, stream);
+  return general_launch<float, float>(resid, delta, delta_bias, delta_weight, delta_eps, extra, vec, rows, weight, out, num_rows, hidden, eps, stream);
+}

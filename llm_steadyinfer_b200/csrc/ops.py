@@ -127,8 +127,8 @@ def _i32(t: Optional[torch.Tensor], name: str) -> None:
 
 # ---------------------------------------------------------------------------------------
 
-def embedding_gather(tokens, table, out, status=None) -> None:
-    """out[t,:] (fp32) = table[tokens[t],:]."""
+def embedding_gather(tokens, table, out, status=None, scale: float = 1.0) -> None:
+    """out[t,:] (fp32) = scale * table[tokens[t],:]."""
     _cuda(tokens, table, out, status)
     _i32(tokens, "tokens")
     _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous(),
@@ -136,8 +136,8 @@ def embedding_gather(tokens, table, out, status=None) -> None:
     T, d = out.shape
     _need(table.shape[1] == d and tokens.numel() == T, "embedding: shape mismatch")
     f = _fn("embedding", "si_embedding_gather",
-            [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p])
-    _check(f(_ptr(tokens), _ptr(table), _dt(table), _ptr(out), T, d, table.shape[0],
+            [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_p])
+    _check(f(_ptr(tokens), _ptr(table), _dt(table), _ptr(out), T, d, table.shape[0], float(scale),
              _ptr(status), _stream()), "embedding_gather")
 
 
@@ -194,6 +194,42 @@ def rmsnorm_rows(x, weight, eps: float, out=None) -> None:
     f = _fn("norm", "si_rmsnorm_rows", [_c_p, _c_p, _c_int, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_f, _c_p])
     _check(f(_ptr(x), _ptr(out), _dt(x), _ptr(weight), _dt(weight), rows, x.shape[-1], inner, xs[0], xs[1], os_[0], os_[1],
              float(eps), _stream()), f"rmsnorm_rows(n={x.shape[-1]})")
+
+
+def add_norm(resid, delta=None, weight=None, eps: float = 0.0, out=None, rows=None, delta_weight=None,
+             delta_eps: float = 0.0, delta_bias=None, extra=None, vec=None) -> None:
+    """The residual add in its general form, all sums and statistics fp32:
+        d = delta (+ delta_bias);  d <- delta_weight * d * rsqrt(mean(d^2) + delta_eps)  (with ``delta_weight``)
+        resid (fp32, in place) += d (+ extra) (+ vec);   out = weight * resid * rsqrt(mean(resid^2) + eps)  (with ``out``)
+    ``extra`` fp32 like resid, ``vec`` and ``delta_bias`` fp32 [hidden]. With ``rows`` (int32 [R]) output row r comes from
+    stream row rows[r] and resid stays as it is."""
+    _cuda(resid, delta, weight, out, rows, delta_weight, delta_bias, extra, vec)
+    _i32(rows, "rows")
+    d = resid.shape[-1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and resid.dim() == 2, "add_norm: resid must be contiguous fp32 rows")
+    if out is not None:
+        _need(weight is not None and weight.is_contiguous() and weight.numel() == d and out.is_contiguous()
+              and out.shape[-1] == d, "add_norm: out needs a weight of the stream's width")
+        _need(out.shape[0] == (rows.numel() if rows is not None else resid.shape[0]), "add_norm: row count mismatch")
+    else:
+        _need(rows is None, "add_norm: rows are for an output")
+    xd = out if out is not None else delta
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.shape == resid.shape and delta.dtype == xd.dtype,
+              "add_norm: delta must match resid's shape and out's dtype")
+    if delta_weight is not None:
+        _need(delta is not None and delta_weight.is_contiguous() and delta_weight.numel() == d
+              and (weight is None or weight.dtype == delta_weight.dtype), "add_norm: delta_weight must be like weight")
+    _f32v(delta_bias, "delta_bias", d); _f32v(vec, "vec", d)
+    if extra is not None:
+        _need(extra.dtype == torch.float32 and extra.is_contiguous() and extra.shape == resid.shape, "add_norm: extra must be like resid")
+    wd = weight if weight is not None else delta_weight
+    R = out.shape[0] if out is not None else resid.shape[0]
+    f = _fn("norm", "si_add_norm_general",
+            [_c_p, _c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_ptr(resid), _ptr(delta), _ptr(delta_bias), _ptr(delta_weight), float(delta_eps), _ptr(extra), _ptr(vec),
+             _ptr(rows), _ptr(weight), _dt(wd) if wd is not None else F32, _ptr(out), _dt(xd) if xd is not None else F32,
+             R, d, float(eps), _stream()), f"add_norm(hidden={d})")
 
 
 def rope_kv_write(qkv, positions, row_seq, inv_freq, rot_dim: int, block_table, k_cache, v_cache,
@@ -854,22 +890,25 @@ def _f32v(t, name: str, n=None) -> None:
 
 def attention_general(q, k_cache, v_cache, block_table, row_seq, positions, out, page_size: int, num_seqs: int,
                       H: int, KV: int, dk: int, dv: int, scale: float, window: int = 0, dist_bias=None, sink=None,
-                      status=None) -> None:
+                      status=None, softcap: float = 0.0, v_share: int = 1) -> None:
     """fp32-arithmetic attention over the paged cache with key size ``dk``, value size ``dv``, values from
     ``v_cache`` or (None) the first ``dv`` entries of the keys, a bias by distance ``dist_bias`` (fp32 [nd, H],
-    row min(distance, nd - 1)) and a sink per head (fp32 [H]) in the softmax denominator."""
+    row min(distance, nd - 1)) and a sink per head (fp32 [H]) in the softmax denominator. ``softcap`` > 0: the scaled
+    score s becomes softcap * tanh(s / softcap). ``v_share`` > 1: that many neighbouring key heads read one value head
+    (``v_cache`` holds KV / v_share heads). ``out`` may be fp32 whatever the storage."""
     _cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, dist_bias, sink, status)
     _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
     T = q.shape[0]
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == H * dk and out.shape[1] == H * dv,
           "attention_general: q must be [T, H*dk], out [T, H*dv]")
-    _need(q.dtype == out.dtype == k_cache.dtype and (v_cache is None or v_cache.dtype == q.dtype),
-          "attention_general: dtypes differ")
+    _need(q.dtype == k_cache.dtype and out.dtype in (q.dtype, torch.float32)
+          and (v_cache is None or v_cache.dtype == q.dtype), "attention_general: dtypes differ")
+    _need(v_share >= 1 and KV % v_share == 0 and (v_share == 1 or v_cache is not None), "attention_general: v_share")
     _need(tuple(k_cache.shape[1:]) == (KV, page_size, dk) and k_cache.is_contiguous(),
           "attention_general: keys must be [pages, KV, page_size, dk]")
     if v_cache is not None:
-        _need(tuple(v_cache.shape) == (k_cache.shape[0], KV, page_size, dv) and v_cache.is_contiguous(),
-              "attention_general: values must be [pages, KV, page_size, dv]")
+        _need(tuple(v_cache.shape) == (k_cache.shape[0], KV // v_share, page_size, dv) and v_cache.is_contiguous(),
+              "attention_general: values must be [pages, KV / v_share, page_size, dv]")
     nd = 0
     if dist_bias is not None:
         _need(dist_bias.dim() == 2 and dist_bias.shape[1] == H, "attention_general: dist_bias must be [nd, H]")
@@ -878,10 +917,11 @@ def attention_general(q, k_cache, v_cache, block_table, row_seq, positions, out,
     _f32v(sink, "sink", H)
     f = _fn("attention_general", "si_attention_general",
             [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p])
+             _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_f, _c_int, _c_int, _c_p, _c_p])
     _check(f(_ptr(q), _dt(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
              _ptr(row_seq), _ptr(positions), _ptr(out), out.stride(0), k_cache.shape[0], page_size, T, num_seqs,
-             H, KV, dk, dv, float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), _ptr(status), _stream()),
+             H, KV, dk, dv, float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), float(softcap or 0.0),
+             int(v_share), 1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0, _ptr(status), _stream()),
            f"attention_general(dk={dk}, dv={dv})")
 
 
@@ -1147,3 +1187,144 @@ def latent_expand_keys(plain, dense, keys, H: int, dq: int, dr: int, rk: int) ->
           "latent_expand_keys: shapes or dtypes")
     f = _fn("attention_general", "si_latent_expand_keys", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
     _check(f(_ptr(plain), _ptr(dense), _ptr(keys), _dt(plain), rows, H, dq, dr, rk, _stream()), "latent_expand_keys")
+
+
+# ---- queries and keys with a norm and a rotation of their own; differential attention -----------------------------
+
+def qk_prepare(rows, q_weight, k_weight, eps: float, inv_freq, rot_dims: int, interleaved: bool, positions, row_seq,
+               block_table, k_cache, v_cache, page_size: int, num_seqs: int, NQ: int, NK: int, NV: int, dk: int, dv: int,
+               status=None, q_out=None, maps: int = 1) -> None:
+    """Rows ``[q: NQ*dk | k: NK*dk | v: NV*dv | ...]`` of a stacked projection: every q and k vector is RMS-normalised
+    (shared fp32 weights ``q_weight``, ``k_weight`` [dk]; None: no norm), its first ``rot_dims`` entries rotated by the
+    row's position (pairs (2i, 2i+1) if ``interleaved``, else (i, i + rot_dims/2); angle pos * inv_freq[i]); q in place
+    or into ``q_out`` [T, NQ*dk], k into ``k_cache`` [pages, NK, page_size, dk], v into ``v_cache`` [pages, NV, page_size, dv]
+    (None: nothing stored). ``maps`` M > 1: the q and k vectors of a head come as M maps, [head][map], and ``q_out`` (needed
+    then) is ordered [key head][map][head of the group], so that query vector i reads key vector i // (NQ / NK)."""
+    _cuda(rows, q_weight, k_weight, inv_freq, positions, row_seq, block_table, k_cache, v_cache, status)
+    _i32(positions, "positions"); _i32(row_seq, "row_seq"); _i32(block_table, "block_table")
+    _need(rows.dim() == 2 and rows.stride(1) == 1 and rows.shape[1] >= (NQ + NK) * dk + NV * dv, "qk_prepare: row layout")
+    _f32v(q_weight, "q_weight", dk); _f32v(k_weight, "k_weight", dk)
+    _f32v(inv_freq, "inv_freq")
+    _need(rot_dims == 0 or (inv_freq is not None and inv_freq.numel() >= rot_dims // 2), "qk_prepare: inv_freq too short")
+    if q_out is None:
+        _need(maps == 1, "qk_prepare: maps need q_out")
+        q_out = rows
+    else:
+        _cuda(q_out)
+        _need(q_out.dtype == rows.dtype and q_out.dim() == 2 and q_out.stride(1) == 1 and q_out.shape == (rows.shape[0], NQ * dk),
+              "qk_prepare: q_out must be [T, NQ*dk]")
+    num_pages = 0
+    if k_cache is not None:
+        _need(k_cache.dtype == rows.dtype and k_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (NK, page_size, dk)
+              and v_cache is not None and v_cache.dtype == rows.dtype and v_cache.is_contiguous()
+              and tuple(v_cache.shape) == (k_cache.shape[0], NV, page_size, dv),
+              "qk_prepare: caches must be [pages, NK, page_size, dk] and [pages, NV, page_size, dv]")
+        num_pages = k_cache.shape[0]
+    f = _fn("qk_prepare", "si_qk_prepare",
+            [_c_p, _c_int, _c_ll, _c_p, _c_p, _c_f, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p])
+    _check(f(_ptr(rows), _dt(rows), rows.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), int(rot_dims),
+             1 if interleaved else 0, _ptr(positions), _ptr(row_seq), _ptr(block_table),
+             block_table.shape[1] if block_table is not None else 0, _ptr(k_cache), _ptr(v_cache), num_pages, page_size,
+             rows.shape[0], int(num_seqs), NQ, NK, NV, dk, dv, _ptr(q_out), q_out.stride(0), int(maps), _ptr(status), _stream()),
+           f"qk_prepare(dk={dk}, dv={dv})")
+
+
+def diff_combine(a, gate, out, H: int, dv: int, ratio: int, lam: float, eps: float, post: float) -> None:
+    """``a`` [T, H*2*dv] (fp32 or the compute dtype) holds the two maps' results in the order [key head][map][head of the
+    group] (``ratio`` heads a key head): per head o = a0 - lam * a1, divided by its root mean square (eps inside the
+    root), times ``post``, times sigmoid(gate[t, h]) (``gate`` [T, H], a strided view; None: no gate); ``out`` [T, H*dv]."""
+    _cuda(a, gate, out)
+    T = a.shape[0]
+    _need(a.shape == (T, H * 2 * dv) and a.stride(1) == 1 and out.shape == (T, H * dv) and out.stride(1) == 1, "diff_combine: shapes")
+    _need(a.dtype in (out.dtype, torch.float32), "diff_combine: dtypes")
+    if gate is not None:
+        _need(gate.shape == (T, H) and gate.stride(1) == 1 and gate.dtype == out.dtype, "diff_combine: gate must be [T, H]")
+    f = _fn("qk_prepare", "si_diff_combine",
+            [_c_p, _c_int, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_f, _c_f, _c_f, _c_p])
+    _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), _dt(out),
+             out.stride(0), T, H, dv, int(ratio), float(lam), float(eps), float(post), _stream()), f"diff_combine(heads={H}, dv={dv})")
+
+
+# ---- gated delta rule ------------------------------------------------------------------------------------------------
+
+def delta_prepare(xc, ba, b_off: int, a_off: int, a_log, dt_bias, bg, G: int, H: int, dk: int, q_scale: float) -> None:
+    """``xc`` fp32 rows [q: G*dk | k: G*dk | ...]: q and k become unit vectors per head (x / sqrt(sum(x^2) + 1e-6)), q times
+    ``q_scale``. ``ba``: rows holding H raw values b at column ``b_off`` and H raw values a at ``a_off``;
+    ``bg`` fp32 [T, 2H] receives beta = sigmoid(b) and g = exp(-exp(a_log) * softplus(a + dt_bias))."""
+    _cuda(xc, ba, a_log, dt_bias, bg)
+    T = xc.shape[0]
+    _need(xc.dtype == torch.float32 and xc.stride(1) == 1 and xc.shape[1] >= 2 * G * dk, "delta_prepare: xc must be fp32 rows")
+    _need(ba.shape[0] == T and ba.stride(1) == 1 and ba.shape[1] >= max(b_off, a_off) + H, "delta_prepare: ba rows")
+    _need(bg.dtype == torch.float32 and bg.is_contiguous() and bg.shape == (T, 2 * H), "delta_prepare: bg must be fp32 [T, 2H]")
+    _f32v(a_log, "a_log", H); _f32v(dt_bias, "dt_bias", H)
+    f = _fn("delta_rule", "si_delta_prepare",
+            [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_ptr(xc), xc.stride(0), _ptr(ba), _dt(ba), ba.stride(0), int(b_off), int(a_off), _ptr(a_log), _ptr(dt_bias),
+             _ptr(bg), T, G, H, dk, float(q_scale), _stream()), f"delta_prepare(heads={H})")
+
+
+def delta_scan(xc, bg, state, y, q_start, ctx_len, slots, num_seqs: int, G: int, H: int, dk: int, dv: int) -> None:
+    """The gated delta rule over every sequence's rows of this step: per head S <- g S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q, from and into the first H*dk*dv floats of ``state[slot]`` (fp32 [H, dk, dv]; from zero
+    for a portion that starts at position 0). ``xc`` fp32 [T, 2*G*dk + H*dv] = [q | k | v] as ``delta_prepare`` leaves
+    it, ``bg`` fp32 [T, 2H], ``y`` fp32 [T, H*dv]. Head h reads q/k head h // (H / G)."""
+    _cuda(xc, bg, state, y, q_start, ctx_len, slots)
+    for t, nm in ((q_start, "q_start"), (ctx_len, "ctx_len"), (slots, "slots")):
+        _i32(t, nm)
+    T = xc.shape[0]
+    _need(xc.dtype == torch.float32 and xc.stride(1) == 1 and xc.shape[1] >= 2 * G * dk + H * dv, "delta_scan: xc must be fp32 [T, 2*G*dk + H*dv]")
+    _need(bg.dtype == torch.float32 and bg.is_contiguous() and bg.shape == (T, 2 * H), "delta_scan: bg must be fp32 [T, 2H]")
+    _need(y.dtype == torch.float32 and y.shape == (T, H * dv) and y.stride(1) == 1, "delta_scan: y must be fp32 [T, H*dv]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= H * dk * dv,
+          "delta_scan: state must be fp32 [slots, >= H*dk*dv]")
+    f = _fn("delta_rule", "si_delta_scan",
+            [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(xc), xc.stride(0), _ptr(bg), _ptr(state), state.stride(0), _ptr(y), y.stride(0), _ptr(q_start),
+             _ptr(ctx_len), _ptr(slots), int(num_seqs), G, H, dk, dv, _stream()), f"delta_scan(heads={H}, dk={dk}, dv={dv})")
+
+
+def head_norm_gate(o, z, weight, out, H: int, dv: int, eps: float) -> None:
+    """out[t, h, :] = weight * o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * silu(z[t, h, :]); ``o`` fp32 [T, H*dv],
+    ``z`` and ``out`` [T, H*dv] in the compute dtype (views with a row stride are fine), ``weight`` fp32 [dv]."""
+    _cuda(o, z, weight, out)
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.shape == (T, H * dv) and o.stride(1) == 1 and z.shape == (T, H * dv)
+          and out.shape == (T, H * dv) and z.stride(1) == 1 and out.stride(1) == 1 and z.dtype == out.dtype,
+          "head_norm_gate: shapes or dtypes")
+    _f32v(weight, "weight", dv)
+    f = _fn("delta_rule", "si_head_norm_gate", [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_ptr(o), o.stride(0), _ptr(z), _dt(z), z.stride(0), _ptr(weight), _ptr(out), out.stride(0), T, H, dv, float(eps),
+             _stream()), f"head_norm_gate(heads={H}, dv={dv})")
+
+
+# ---- small elementwise steps -----------------------------------------------------------------------------------------
+
+def softcap(x, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (contiguous fp32)."""
+    _cuda(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "softcap: contiguous fp32 only")
+    f = _fn("activation", "si_softcap", [_c_p, _c_ll, _c_f, _c_p])
+    _check(f(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+def add_bias(x, bias) -> None:
+    """x[t, :] += bias (fp32 [width]) in place; rows may have a stride."""
+    _cuda(x, bias)
+    _need(x.dim() == 2 and x.stride(1) == 1, "add_bias: x must be rows")
+    _f32v(bias, "bias", x.shape[1])
+    f = _fn("activation", "si_add_bias", [_c_p, _c_ll, _c_int, _c_p, _c_int, _c_int, _c_p])
+    _check(f(_ptr(x), x.stride(0), _dt(x), _ptr(bias), x.shape[0], x.shape[1], _stream()), "add_bias")
+
+
+def glu_limited(gu, bias, out, group, limit: float, alpha: float) -> None:
+    """out[t, f] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate + bias, limit), u = clamp(up + bias, -limit, limit);
+    ``gu`` [T, 2F] holds gate and up interleaved in groups of ``group`` columns (None: F), ``bias`` fp32 [2F] in the same
+    order or None."""
+    _cuda(gu, bias, out)
+    T, F = out.shape
+    _need(gu.shape == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous() and gu.dtype == out.dtype, "glu_limited: gu must be [T, 2F]")
+    _f32v(bias, "bias", 2 * F)
+    f = _fn("swiglu", "si_glu_limited", [_c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_f, _c_p])
+    _check(f(_ptr(gu), _ptr(bias), _ptr(out), _dt(out), T, F, F if group is None else int(group), float(limit), float(alpha),
+             _stream()), f"glu_limited(F={F})")

@@ -1,0 +1,179 @@
+// What stands between a stacked q/k/v projection and attention over the paged cache when queries and keys are
+// normalised per vector and rotated in part, and when several key vectors share one value vector:
+//   row = [ q: NQ vectors of dk | k: NK vectors of dk | v: NV vectors of dv | ... ]
+//   x  <- w * x * rsqrt(mean(x^2) + eps)          every q and k vector, w shared by all (w absent: no norm)
+//   x  <- rotate(x)                               the first rd entries: pairs (2i, 2i + 1) ("interleaved") or
+//                                                 (i, i + rd/2) ("halves"), angle pos * inv_freq[i], all in fp32:
+//                                                 (u, v) -> (u cos a - v sin a, v cos a + u sin a); the rest pass
+//   q into `q_out` (which may be the rows themselves); k into the key pages [pages, NK, page_size, dk]; v as it is
+//   into the value pages [pages, NV, page_size, dv].
+// With `maps` M > 1 the vectors of a head come as M maps, [head][map], and map m of a head reads key vector
+// (key head, m): q_out is then ordered [key head][map][head of the group], so that query vector i reads key vector
+// i / (NQ / NK) as in any grouped attention (q_out must not be the rows then).
+// One block a token row, one warp a vector. The second kernel of the file combines the maps of a differential
+// attention (see there).
+#include "common.cuh"
+#include <math.h>
+
+template <typename T>
+__device__ __forceinline__ void norm_rotate_vector(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ w,
+                                                   float eps, const float* __restrict__ inv_freq, int rd, int interleaved,
+                                                   float fpos, int dk, int lane) {
+  float inv = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+      const float x = to_f32<T>(src[i]);
+      ss += x * x;
+    }
+    inv = rsqrtf(warp_sum(ss) / (float)dk + eps);
+  }
+  const int half = rd / 2;
+  // every entry is read (with its partner) before any entry of the vector is written: in place is safe only
+  // because a lane's results are kept until the warp has read everything
+  float keep[20];
+#pragma unroll
+  for (int c = 0; c < 20; ++c) {
+    const int i = lane + 32 * c;
+    if (i >= dk) break;
+    float y = to_f32<T>(src[i]) * inv * (w ? w[i] : 1.f);
+    if (i < rd) {
+      int f, partner;
+      bool first;
+      if (interleaved) { f = i >> 1; first = (i & 1) == 0; partner = i ^ 1; }
+      else { first = i < half; f = first ? i : i - half; partner = first ? i + half : i - half; }
+      const float z = to_f32<T>(src[partner]) * inv * (w ? w[partner] : 1.f);
+      float s, c2;
+      sincosf(fpos * inv_freq[f], &s, &c2);
+      y = first ? y * c2 - z * s : y * c2 + z * s;
+    }
+    keep[c] = y;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < 20; ++c) {
+    const int i = lane + 32 * c;
+    if (i >= dk) break;
+    dst[i] = from_f32<T>(keep[c]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const float* __restrict__ q_w,
+    const float* __restrict__ k_w, float eps, const float* __restrict__ inv_freq, int rd, int interleaved,
+    const int* __restrict__ positions, const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_width,
+    T* __restrict__ k_cache, T* __restrict__ v_cache, int num_pages, int page_size, int num_seqs, int NQ, int NK, int NV,
+    int dk, int dv, T* __restrict__ q_out, long long q_out_stride, int maps, int* status) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int pos = positions[t];
+  const int seq = row_seq[t];
+  if (seq < 0) return;                               // a padding row of a fixed-shape step
+  if (seq >= num_seqs) {
+    if (threadIdx.x == 0) set_status(status, SI_BAD_SEQ);
+    return;
+  }
+  long long page = -1;
+  if (k_cache) {
+    const int slot = pos / page_size;
+    page = (pos >= 0 && slot < table_width) ? block_table[(size_t)seq * table_width + slot] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) set_status(status, SI_BAD_PAGE);
+      page = -1;
+    }
+  }
+  const int off = pos % page_size;
+  T* row = rows + (size_t)t * row_stride;
+  const float fpos = (float)pos;
+  const int ratio = NQ / NK;                         // query vectors a key vector
+  for (int vec = warp; vec < NQ + NK; vec += nwarps) {
+    T* src = row + (size_t)vec * dk;
+    if (vec < NQ) {
+      const int head = vec / maps, m = vec - head * maps;
+      const int place = ((head / ratio) * maps + m) * ratio + head % ratio;       // maps == 1: vec itself
+      norm_rotate_vector<T>(src, q_out + (size_t)t * q_out_stride + (size_t)place * dk, q_w, eps, inv_freq, rd, interleaved,
+                            fpos, dk, lane);
+    } else if (page >= 0) {
+      T* dst = k_cache + (((size_t)page * NK + (vec - NQ)) * page_size + off) * dk;
+      norm_rotate_vector<T>(src, dst, k_w, eps, inv_freq, rd, interleaved, fpos, dk, lane);
+    }
+  }
+  if (page >= 0 && v_cache) {
+    const T* vrow = row + (size_t)(NQ + NK) * dk;
+    for (int idx = threadIdx.x; idx < NV * dv; idx += blockDim.x) {
+      const int g = idx / dv, c = idx % dv;
+      v_cache[(((size_t)page * NV + g) * page_size + off) * dv + c] = vrow[idx];
+    }
+  }
+}
+
+SI_EXPORT int si_qk_prepare(void* rows, int dtype, long long row_stride, const float* q_w, const float* k_w, float eps,
+                            const float* inv_freq, int rd, int interleaved, const int* positions, const int* row_seq,
+                            const int* block_table, int table_width, void* k_cache, void* v_cache, int num_pages,
+                            int page_size, int num_tokens, int num_seqs, int NQ, int NK, int NV, int dk, int dv, void* q_out,
+                            long long q_out_stride, int maps, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (dk <= 0 || dk > 640 || rd < 0 || rd > dk || rd % 2 || (rd > 0 && !inv_freq)) return -2;
+  if (maps < 1 || NK <= 0 || NQ % NK || NK % maps || (maps > 1 && q_out == rows)) return -2;
+  if (dtype == SI_BF16)
+    si_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, stream, (__nv_bfloat16*)rows, row_stride, q_w,
+              k_w, eps, inv_freq, rd, interleaved, positions, row_seq, block_table, table_width, (__nv_bfloat16*)k_cache,
+              (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, NQ, NK, NV, dk, dv, (__nv_bfloat16*)q_out, q_out_stride,
+              maps, status);
+  else
+    si_launch(qk_prepare_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, (float*)rows, row_stride, q_w, k_w, eps,
+              inv_freq, rd, interleaved, positions, row_seq, block_table, table_width, (float*)k_cache, (float*)v_cache,
+              num_pages, page_size, num_seqs, NQ, NK, NV, dk, dv, (float*)q_out, q_out_stride, maps, status);
+  return si_last_error();
+}
+
+// ---- the maps of a differential attention into one head ------------------------------------------------------------
+//   a[t, g, m, hl]: the maps' results (dv each, fp32 or the compute dtype) in the order the prepared queries have:
+//   key head g, map m, head hl of the group (`ratio` heads a key head); head h = g * ratio + hl
+//   o = a0 - lambda * a1;   o <- o * rsqrt(mean(o^2) + eps) * post;   o <- o * sigmoid(gate[t, h])   (gate absent: none)
+// One warp a (row, head); everything in fp32.
+template <typename TA, typename T>
+__global__ void __launch_bounds__(256) diff_combine_kernel(const TA* __restrict__ a, long long a_stride, const T* __restrict__ gate,
+    long long gate_stride, T* __restrict__ out, long long out_stride, long long pairs, int H, int dv, int ratio, float lambda,
+    float eps, float post) {
+  pdl_prologue();
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = w / H;
+  const int h = (int)(w - t * H);
+  const TA* a0 = a + t * a_stride + ((size_t)(h / ratio) * 2 * ratio + h % ratio) * dv;
+  const TA* a1 = a0 + (size_t)ratio * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) {
+    const float o = to_f32<TA>(a0[i]) - lambda * to_f32<TA>(a1[i]);
+    ss += o * o;
+  }
+  ss = warp_sum(ss);
+  float f = rsqrtf(ss / (float)dv + eps) * post;
+  if (gate) f *= 1.f / (1.f + expf(-to_f32<T>(gate[t * gate_stride + h])));
+  T* o = out + t * out_stride + (size_t)h * dv;
+  for (int i = lane; i < dv; i += 32) o[i] = from_f32<T>((to_f32<TA>(a0[i]) - lambda * to_f32<TA>(a1[i])) * f);
+}
+
+SI_EXPORT int si_diff_combine(const void* a, int a_dtype, long long a_stride, const void* gate, long long gate_stride, void* out,
+                              int dtype, long long out_stride, int rows, int H, int dv, int ratio, float lambda, float eps,
+                              float post, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || dv <= 0 || ratio <= 0 || H % ratio) return -2;
+  const long long pairs = (long long)rows * H;
+  const dim3 grid((unsigned)((pairs + 7) / 8)), block(256);
+  if (dtype == SI_BF16 && a_dtype == SI_F32)
+    si_launch(diff_combine_kernel<float, __nv_bfloat16>, grid, block, 0, stream, (const float*)a, a_stride,
+              (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride, pairs, H, dv, ratio, lambda, eps, post);
+  else if (dtype == SI_BF16 && a_dtype == SI_BF16)
+    si_launch(diff_combine_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)a, a_stride,
+              (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride, pairs, H, dv, ratio, lambda, eps, post);
+  else if (dtype == SI_F32 && a_dtype == SI_F32)
+    si_launch(diff_combine_kernel<float, float>, grid, block, 0, stream, (const float*)a, a_stride, (const float*)gate,
+              gate_stride, (float*)out, out_stride, pairs, H, dv, ratio, lambda, eps, post);
+  else
+    return -2;
+  return si_last_error();
+}

@@ -81,3 +81,41 @@ SI_EXPORT int si_swiglu(const void* gu, void* out, int dtype, int num_tokens, in
   }
   return si_last_error();
 }
+
+// The gated activation with limits: with g and u the gate and up columns of a row (interleaved in groups as above)
+// plus their biases (fp32, in the stacked order of the columns; may be absent),
+//   g <- min(g, limit);  u <- clamp(u, -limit, limit);  out = g * sigmoid(alpha * g) * (u + 1)
+// in fp32. One thread an output element.
+template <typename T>
+__global__ void glu_limited_kernel(const T* __restrict__ gu, const float* __restrict__ bias, T* __restrict__ out, int F,
+                                   int group, float limit, float alpha, long long total) {
+  pdl_prologue();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / F;
+    const int f = (int)(idx - t * F);
+    const T* row = gu + (size_t)t * 2 * F;
+    const int gc = (f / group) * 2 * group + f % group;
+    float g = to_f32<T>(row[gc]), u = to_f32<T>(row[gc + group]);
+    if (bias) { g += bias[gc]; u += bias[gc + group]; }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    out[idx] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+SI_EXPORT int si_glu_limited(const void* gu, const float* bias, void* out, int dtype, int num_tokens, int F, int group,
+                             float limit, float alpha, cudaStream_t stream) {
+  const long long total = (long long)num_tokens * F;
+  if (total <= 0) return 0;
+  if (group <= 0 || F % group) return -2;
+  const int threads = 256;
+  const long long want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 16LL * si_sm_count() ? want : 16LL * si_sm_count());
+  if (dtype == SI_BF16)
+    si_launch(glu_limited_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gu, bias,
+              (__nv_bfloat16*)out, F, group, limit, alpha, total);
+  else
+    si_launch(glu_limited_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, bias, (float*)out, F,
+              group, limit, alpha, total);
+  return si_last_error();
+}

@@ -1,2 +1,2 @@
-from . import llama, mivorax  # noqa: F401  (register "LlamaForCausalLM", "Mivorax")
+from . import llama, mivorax, nufasun  # noqa: F401  (register "LlamaForCausalLM", "Mivorax", "Nufasun")
 from .model import Model

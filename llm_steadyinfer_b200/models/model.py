@@ -14,7 +14,7 @@ import torch
 
 from ..config.base import EmbedderSpec, ModelConfig, ModelSpec
 from ..csrc import ops
-from ..parts import Block, embedder_class, feed_forward_class, mixer_class, norm_class, position_class
+from ..parts import Block, NormedDelta, embedder_class, feed_forward_class, mixer_class, norm_class, position_class
 from ..parts.linear import configure_library_gemm, linear
 from ..engine import tracing
 
@@ -39,7 +39,12 @@ class Model:
                 ffn = feed_forward_class(ls.feed_forward.kind)(ls.feed_forward.params, dtype, self.device)
                 n2 = norm_class(ls.feed_forward_norm.kind)(ls.feed_forward_norm.params, dtype, self.device)
             n1 = norm_class(ls.mixer_norm.kind)(ls.mixer_norm.params, dtype, self.device)
-            self.blocks.append(Block(mixer, ffn, n1, n2, ls.arrangement))
+            n1b = n2b = None                          # norms behind the sublayers, where the layer has them
+            if ls.mixer_post_norm is not None:
+                n1b = norm_class(ls.mixer_post_norm.kind)(ls.mixer_post_norm.params, dtype, self.device)
+            if ffn is not None and ls.feed_forward_post_norm is not None:
+                n2b = norm_class(ls.feed_forward_post_norm.kind)(ls.feed_forward_post_norm.params, dtype, self.device)
+            self.blocks.append(Block(mixer, ffn, n1, n2, ls.arrangement, n1b, n2b))
         self.final_norm = norm_class(self.spec.final_norm.kind)(self.spec.final_norm.params, dtype, self.device)
         # the embedder: by default the plain table under the spec's embedding name
         es = self.spec.embedder or EmbedderSpec("table", {})
@@ -51,6 +56,13 @@ class Model:
         self.embed: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
         self._layer_hook = None
+        # what the stream gains between layers: place of the run order -> spec; the vectors come with the weights
+        self.stream_adds = {a.place: a for a in self.spec.stream_adds}
+        self.stream_vectors: Dict[str, torch.Tensor] = {}
+        self._keeps_embedding = any(a.embedding for a in self.spec.stream_adds)
+        for a in self.spec.stream_adds:
+            if not 0 <= a.place < len(self.spec.order):
+                raise ValueError(f"a stream addition names place {a.place} of a run order of {len(self.spec.order)}")
         for i in self.spec.order:
             if not 0 <= i < len(self.blocks):
                 raise ValueError(f"run order names layer {i}, but the model has {len(self.blocks)} layers")
@@ -61,9 +73,13 @@ class Model:
             p = ls.weight_prefix
             yield p + ls.mixer_prefix, b.mixer
             yield p + ls.mixer_norm_name, b.mixer_norm
+            if b.mixer_post_norm is not None:
+                yield p + ls.mixer_post_norm_name, b.mixer_post_norm
             if b.feed_forward is not None:
                 yield p + ls.feed_forward_prefix, b.feed_forward
                 yield p + ls.feed_forward_norm_name, b.feed_forward_norm
+                if b.feed_forward_post_norm is not None:
+                    yield p + ls.feed_forward_post_norm_name, b.feed_forward_post_norm
         yield self.spec.final_norm_name, self.final_norm
         yield self._embed_prefix, self.embedder
 
@@ -75,6 +91,8 @@ class Model:
         for prefix, part in self._named_parts():
             for n, s in part.weight_shapes().items():
                 shapes[prefix + n] = tuple(s)
+        for n, s in (self.spec.stream_vector_shapes or {}).items():
+            shapes[n] = tuple(s)
         return shapes
 
     def optional_weights(self) -> List[str]:
@@ -82,6 +100,8 @@ class Model:
         return [self.spec.lm_head_name] if self.spec.tie_word_embeddings else []
 
     def keeps_dtype(self, name: str) -> bool:
+        if name in (self.spec.stream_vector_shapes or {}):
+            return True
         for prefix, part in self._named_parts():
             if name.startswith(prefix) and name[len(prefix):] in part.weight_shapes():
                 return part.keeps_dtype(name[len(prefix):])
@@ -100,12 +120,15 @@ class Model:
         compute dtype."""
         for prefix, part in self._named_parts():
             part.load_weights({n: tensors[prefix + n] for n in part.weight_shapes()})
+        self.stream_vectors = {n: tensors[n].float().contiguous() for n in (self.spec.stream_vector_shapes or {})}
         self.embed = self.embedder.table
         self.lm_head = self.embed if self.spec.tie_word_embeddings else tensors[self.spec.lm_head_name].contiguous()
 
     def kernel_files(self, page_size: int) -> List[str]:
         """CUDA sources of the model's own kernels and of its parts (see ``Part.kernel_files``)."""
         names = {"sampling"} | ({"gemm_f32"} if self.dtype == torch.float32 else {"gemm_skinny", "gemm_rows", "gemm_tc05"})
+        if self.spec.logit_softcap > 0:
+            names.add("activation")
         for _, part in self._named_parts():
             names.update(part.kernel_files(page_size))
         return sorted(names)
@@ -141,15 +164,25 @@ class Model:
         T, d = ctx.num_tokens, self.spec.hidden_size
         resid = ctx.buf("resid", (T, d), torch.float32)
         self.embedder.forward(ctx, resid, caches[len(self.spec.order)].state)
+        embed_out = None
+        if self._keeps_embedding:
+            embed_out = ctx.buf("embed_out", (T, d), torch.float32)
+            embed_out.copy_(resid)
         delta = None
         for o, i in enumerate(self.spec.order):
+            add = self.stream_adds.get(o)
+            if add is not None:                       # the pending delta goes in with what the stream gains here
+                vec = self.stream_vectors[add.vector_name][add.row] if add.vector_name is not None else None
+                self._stream_add(resid, delta, embed_out if add.embedding else None, vec)
+                delta = None
             if tracing.ENABLED:
                 with tracing.span(f"layer {i}"):
                     delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
             else:
                 delta = self.blocks[i].forward(resid, delta, ctx, caches[o])
             if self._layer_hook is not None:
-                self._layer_hook(o, resid if delta is None else resid + delta.float())
+                self._layer_hook(o, resid if delta is None else resid + (
+                    delta.value() if isinstance(delta, NormedDelta) else delta.float()))
         R = ctx.num_logit_rows
         if R == 0:
             return None
@@ -157,4 +190,15 @@ class Model:
         self.final_norm.forward(resid, delta, x, rows=ctx.logit_rows)
         logits = ctx.buf("logits", (R, self.spec.vocab_size), torch.float32)
         linear(x, self.lm_head, logits, ctx.status)
+        if self.spec.logit_softcap > 0:
+            ops.softcap(logits, self.spec.logit_softcap)
         return logits
+
+    @staticmethod
+    def _stream_add(resid, delta, extra, vec) -> None:
+        """``resid += delta (+ extra) (+ vec)`` in one launch; ``delta`` may be None, a tensor or a ``NormedDelta``."""
+        if isinstance(delta, NormedDelta):
+            ops.add_norm(resid, delta.x, delta_weight=delta.norm.weight, delta_eps=delta.norm.eps, delta_bias=delta.bias,
+                         extra=extra, vec=vec)
+        elif delta is not None or extra is not None or vec is not None:
+            ops.add_norm(resid, delta, extra=extra, vec=vec)

@@ -41,19 +41,26 @@ class CacheNeed:
     """Paged keys and values of one layer: pages of [num_kv_heads, page_size, head_dim] for keys and
     [num_kv_heads, page_size, value_dim] for values. ``window`` None keeps every token; otherwise pages
     that lie wholly before ``position - window + 1`` are given back. ``value_dim`` None: as ``head_dim``;
-    0: the layer keeps no values of their own (a latent that serves as key and value)."""
+    0: the layer keeps no values of their own (a latent that serves as key and value). ``num_value_heads`` None:
+    as many value heads as key heads; otherwise the value pages hold that many heads (several key heads that read
+    one value head, as the maps of a differential attention do)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
+    num_value_heads: Optional[int] = None
 
     @property
     def v_dim(self) -> int:
         return self.head_dim if self.value_dim is None else int(self.value_dim)
 
+    @property
+    def v_heads(self) -> int:
+        return self.num_kv_heads if self.num_value_heads is None else int(self.num_value_heads)
+
     def layout_key(self) -> Tuple:
         """What two layers must share for one to read the other's pages."""
-        return ("paged_kv", self.num_kv_heads, self.head_dim, self.v_dim)
+        return ("paged_kv", self.num_kv_heads, self.head_dim, self.v_dim, self.v_heads)
 
     def group_key(self) -> Tuple:
         return self.layout_key() + (self.window,)
@@ -65,6 +72,23 @@ class StateNeed:
     slot, zeroed when a request is admitted."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class NormedDelta:
+    """A sublayer's result that is still to be normalised before it joins the residual stream (a block with a norm
+    behind each sublayer): ``x`` [T, d] in the compute dtype, ``norm`` the norm to apply (its weight and eps are what
+    the adding kernel takes), ``bias`` an fp32 [d] vector that belongs to ``x`` before the norm (the bias of the
+    product that made it) or None. A norm's ``forward`` that is given one as ``delta`` normalises and adds it in the
+    same launch as its own norm; ``value()`` is the plain fp32 result for hooks and tests."""
+    x: torch.Tensor
+    norm: "Norm"
+    bias: Optional[torch.Tensor] = None
+
+    def value(self) -> torch.Tensor:
+        d = self.x.float() if self.bias is None else self.x.float() + self.bias
+        w = self.norm.weight.float()
+        return d * torch.rsqrt((d * d).mean(-1, keepdim=True) + self.norm.eps) * w
 
 
 class Part:

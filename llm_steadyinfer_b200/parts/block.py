@@ -9,6 +9,10 @@ kernel), and returns its own pending delta, which the block after it (or the fin
 The built-in "pre_norm" is the reference's block (src/source/model/llama3.cpp:996-1181):
     h += delta_in;  x = norm1(h);  a = mixer(x);  h += a;  x = norm2(h);  return ffn(x)
 (a block whose spec has no feed-forward ends after the mixer and returns ``a``).
+"sandwich" has a norm behind each sublayer as well as before it:
+    h += delta_in;  a = mixer(norm1(h));  h += norm1b(a);  f = ffn(norm2(h));  return norm2b(f), still to be added
+What it hands on is a ``NormedDelta``: the sublayer's raw result with the norm that belongs to it, which the next
+norm's launch normalises and adds before its own statistics (no launch of its own).
 Another arrangement (post-norm, parallel mixer and feed-forward, ...) is added with
 ``register_arrangement`` and needs no change here.
 """
@@ -18,7 +22,7 @@ from typing import Callable, Dict, Optional
 
 import torch
 
-from .base import FeedForward, Mixer, Norm
+from .base import FeedForward, Mixer, Norm, NormedDelta
 
 _ARRANGEMENTS: Dict[str, Callable] = {}
 _CAPTURABLE: Dict[str, bool] = {}
@@ -41,11 +45,14 @@ def arrangement(name: str) -> Callable:
 
 class Block:
     def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm,
-                 feed_forward_norm: Optional[Norm], arrangement_name: str = "pre_norm"):
+                 feed_forward_norm: Optional[Norm], arrangement_name: str = "pre_norm",
+                 mixer_post_norm: Optional[Norm] = None, feed_forward_post_norm: Optional[Norm] = None):
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
         self.feed_forward_norm = feed_forward_norm
+        self.mixer_post_norm = mixer_post_norm
+        self.feed_forward_post_norm = feed_forward_post_norm
         self.arrangement = arrangement_name
         self._run = arrangement(arrangement_name)
         self.capturable = _CAPTURABLE[arrangement_name]
@@ -81,3 +88,23 @@ def pre_norm(block: Block, resid, delta, ctx, cache):
 
 
 register_arrangement("pre_norm", pre_norm, capturable=True)
+
+
+def sandwich(block: Block, resid, delta, ctx, cache):
+    if block.mixer_post_norm is None or (block.feed_forward is not None and block.feed_forward_post_norm is None):
+        raise ValueError("arrangement 'sandwich' needs a norm behind each sublayer")
+    T, d = resid.shape
+    x = ctx.buf("block_x", (T, d), block.mixer.dtype)
+    block.norm(block.mixer_norm, resid, delta, x)
+    a = NormedDelta(block.mixer.forward(x, ctx, cache), block.mixer_post_norm)
+    if block.feed_forward is None:
+        return a
+    block.norm(block.feed_forward_norm, resid, a, x)
+    ff = block.feed_forward
+    bias = getattr(ff, "output_bias", None)
+    if bias is not None:                                  # the last product's bias joins the result inside the adding kernel
+        return NormedDelta(ff.forward(x, ctx, add_bias=False), block.feed_forward_post_norm, bias)
+    return NormedDelta(ff.forward(x, ctx), block.feed_forward_post_norm)
+
+
+register_arrangement("sandwich", sandwich, capturable=True)

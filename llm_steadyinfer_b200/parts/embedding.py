@@ -1,6 +1,7 @@
 """Embedders: the step's tokens into rows of the fp32 residual stream.
 
-``table``        ``x = table[token]``: the reference's embedding (src/source/op/kernels/cuda/emb_kernel.cu:3-21).
+``table``        ``x = scale * table[token]`` (``scale`` 1 unless given): the reference's embedding
+                 (src/source/op/kernels/cuda/emb_kernel.cu:3-21) has no scale.
 ``table_pair``   ``x = table[token] + pair[r]`` with a hashed embedding of the pair (previous token, token):
                  ``r = (previous * mul_prev + token * mul_cur) mod buckets``; the first token of a sequence takes
                  the pair table's extra last row, number ``buckets``. The previous token of a portion's first row is
@@ -23,6 +24,7 @@ class TableEmbedder(Embedder):
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.name = params.get("name", "weight")
+        self.scale = float(params.get("scale", 1.0))
 
     def weight_shapes(self):
         return {self.name: (self.vocab, self.hidden)}
@@ -34,7 +36,7 @@ class TableEmbedder(Embedder):
         return ("embedding",)
 
     def forward(self, ctx, out, state):
-        ops.embedding_gather(ctx.tokens, self.table, out, status=ctx.status)
+        ops.embedding_gather(ctx.tokens, self.table, out, status=ctx.status, scale=self.scale)
 
 
 class TablePairEmbedder(TableEmbedder):
@@ -44,6 +46,8 @@ class TablePairEmbedder(TableEmbedder):
         self.mul_prev = int(params["mul_prev"])
         self.mul_cur = int(params["mul_cur"])
         self.pair_name = params.get("pair_name", "pair")
+        if self.scale != 1.0:
+            raise ValueError("table_pair: a scale on the embedding is not supported")
         if self.buckets <= 0 or self.mul_prev < 0 or self.mul_cur < 0:
             raise ValueError("table_pair: buckets must be positive and the multipliers not negative")
         self.pair = None

@@ -131,3 +131,71 @@ class DenseMLP(FeedForward):
 
 
 register_feed_forward("dense_mlp", DenseMLP)
+
+
+class LimitedGatedMLP(FeedForward):
+    """Gated feed-forward with limits and biases:
+        g = min(W_gate x + b_gate, limit);  u = clamp(W_up x + b_up, -limit, limit)
+        y = g * sigmoid(alpha * g) * (u + 1);  out = W_down y + b_down
+    ``limit`` and ``alpha`` (default 1.702, which makes g * sigmoid(alpha g) close to gelu) are parameters; so are the
+    tensor names (``names``: gate, up, down; each bias is the matrix's name + ``bias_suffix``). gate and up are
+    stacked and interleaved as in ``GatedMLP``. The activation is fp32 arithmetic on the product's stored result.
+    ``output_bias`` is the down projection's bias; a caller that adds it itself (an arrangement that normalises the
+    result anyway) calls ``forward(..., add_bias=False)``."""
+    capturable = True
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.limit = float(params["limit"])
+        self.alpha = float(params.get("alpha", 1.702))
+        if not self.limit > 0:
+            raise ValueError(f"gated_mlp_limited: limit must be positive, found {self.limit}")
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(params.get("names") or {})
+        self.bias_suffix = params.get("bias_suffix", ".bias")
+        self.group = INTERLEAVE if self.inter % INTERLEAVE == 0 else self.inter
+        self.gate_up = self.down = self.gate_up_bias = self.output_bias = None
+
+    def weight_shapes(self):
+        n, b = self.names, self.bias_suffix
+        return {n["gate"]: (self.inter, self.hidden), n["up"]: (self.inter, self.hidden), n["down"]: (self.hidden, self.inter),
+                n["gate"] + b: (self.inter,), n["up"] + b: (self.inter,), n["down"] + b: (self.hidden,)}
+
+    def keeps_dtype(self, name):
+        return name.endswith(self.bias_suffix) and name[:-len(self.bias_suffix)] in self.names.values()
+
+    def norm_like(self, name):
+        return False
+
+    def load_weights(self, tensors):
+        n, b = self.names, self.bias_suffix
+        k = self.inter // self.group
+        stack = lambda g, u, *rest: torch.stack([g.view(k, self.group, *rest), u.view(k, self.group, *rest)], 1)
+        self.gate_up = stack(tensors[n["gate"]], tensors[n["up"]], self.hidden).reshape(2 * self.inter, self.hidden).contiguous()
+        self.gate_up_bias = stack(tensors[n["gate"] + b].float(), tensors[n["up"] + b].float()).reshape(2 * self.inter).contiguous()
+        self.down = tensors[n["down"]].contiguous()
+        self.output_bias = tensors[n["down"] + b].float().contiguous()
+
+    def streams_first(self, rows):
+        return self.gate_up if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
+
+    def kernel_files(self, page_size):
+        return ("gemm_f32", "swiglu", "activation") if self.dtype == torch.float32 else \
+            ("gemm_skinny", "swiglu", "activation", "gemm_tc05", "gemm_rows")
+
+    def forward(self, x, ctx, add_bias=True):
+        T = x.shape[0]
+        gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
+        linear(x, self.gate_up, gu, ctx.status)
+        act = ctx.buf("ffn_act", (T, self.inter), self.dtype)
+        ops.glu_limited(gu, self.gate_up_bias, act, self.group, self.limit, self.alpha)
+        out = ctx.buf("delta", (T, self.hidden), self.dtype)
+        linear(act, self.down, out, ctx.status)
+        if add_bias:
+            ops.add_bias(out, self.output_bias)
+        return out
+
+
+register_feed_forward("gated_mlp_limited", LimitedGatedMLP)

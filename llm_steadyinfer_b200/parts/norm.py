@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 from ..csrc import ops
-from .base import Norm, register_norm
+from .base import Norm, NormedDelta, register_norm
 
 
 class RMSNorm(Norm):
@@ -37,7 +37,16 @@ class RMSNorm(Norm):
         return ("norm",)
 
     def forward(self, resid, delta, out, rows=None, ahead=None):
-        ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows, ahead=ahead)
+        if isinstance(delta, NormedDelta):           # the sublayer before has a norm of its own behind it
+            ops.add_norm(resid, delta.x, self.weight, self.eps, out, rows=rows, delta_weight=delta.norm.weight,
+                         delta_eps=delta.norm.eps, delta_bias=delta.bias)
+        else:
+            ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows, ahead=ahead)
+
+    def add(self, resid, delta: NormedDelta, extra=None, vec=None):
+        """``resid += norm(delta) (+ extra) (+ vec)`` with no norm of the stream behind it."""
+        ops.add_norm(resid, delta.x, delta_weight=delta.norm.weight, delta_eps=delta.norm.eps, delta_bias=delta.bias,
+                     extra=extra, vec=vec)
 
     def normalize(self, x, out=None):
         ops.rmsnorm_rows(x, self.weight, self.eps, out)
