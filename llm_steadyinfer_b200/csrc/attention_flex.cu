@@ -1,8 +1,10 @@
 // bf16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, fp32 accumulation, fp32 online
 // softmax) in the general form of attention_general.cu: key size dk and value size dv of any multiple of 8,
 // values of their own or the first dv entries of the keys (a latent that is key and value), a bias by distance
-// added to the scaled score, a sink per head in the denominator. One kernel serves prompt portions and decode
-// rows; for decode the key range of an item can be split over blocks, whose fp32 partial results a second small
+// added to the scaled score, a sink per head in the denominator, a soft limit on the scaled score
+// (s <- cap * tanh(s / cap)), key heads that share a value head (v_share neighbouring key heads read one of the
+// KV / v_share value heads), results in fp32 where the caller goes on computing with them. One kernel serves prompt
+// portions and decode rows; for decode the key range of an item can be split over blocks, whose fp32 partial results a second small
 // kernel merges.
 //
 // A work item is a run of consecutive query tokens of one sequence. A block handles one item, one KV head, one
@@ -21,6 +23,9 @@ struct FlexParams {
   const int* block_table; int table_width;
   const AttnItem* items; int num_items;
   bf16* out; long long out_stride;
+  float* out_f32;           // not null: results go here as fp32 (same strides), not to `out`
+  float cap_log2, scale_over_cap;   // soft limit: cap * log2(e) and scale / cap (cap_log2 0: none)
+  int v_share;              // key heads that read one value head
   float* part_o;            // [item][gy][split][64 rows][dv]   (nsplit > 1)
   float* part_ml;           // [item][gy][split][64 rows][2]
   const float* dist_bias; int nd;                // fp32 [nd, H] or nullptr
@@ -114,6 +119,10 @@ attn_flex_kernel(const FlexParams p) {
     }
     if (own_v) {
       bf16* Vt = Vs + (size_t)stage * BLOCK_N * DVB;
+      if (in_range && p.v_share > 1) {           // the value head that this key head shares with its neighbours
+        const int slot = j / p.page_size;
+        tok = ((size_t)table[slot] * (p.KV / p.v_share) + g / p.v_share) * p.page_size + (j - slot * p.page_size);
+      }
       const bf16* vrow = p.v_cache + tok * p.dv + v0;
       for (int c = c_first; c < DT; c += TPR) {
         const bool valid = in_range && v0 + c * 8 < p.dv;
@@ -210,7 +219,7 @@ attn_flex_kernel(const FlexParams p) {
           const bool vis = j >= kv_lo && j <= pos && (p.window <= 0 || j > pos - p.window);
           float v = -INFINITY;
           if (vis) {
-            v = s[nt][e] * p.scale_log2;
+            v = p.cap_log2 > 0.f ? p.cap_log2 * tanhf(s[nt][e] * p.scale_over_cap) : s[nt][e] * p.scale_log2;
             if (p.bias_in_smem) v += Bt[(pos - j - dlo) * p.Gb + ((e < 2) ? hh_lo : hh_hi)];
             else if (p.dist_bias) v += p.dist_bias[(size_t)min(pos - j, p.nd - 1) * p.H + ((e < 2) ? head_lo : head_hi)] * LOG2E;
           }
@@ -339,12 +348,13 @@ attn_flex_kernel(const FlexParams p) {
       l = l * f + exp2f(s2 - M);
     }
     const float inv = l > 0.f ? f / l : 0.f;
-    bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)(head0 + hh) * p.dv;
+    const size_t at = (size_t)(item.row0 + tok) * p.out_stride + (size_t)(head0 + hh) * p.dv;
 #pragma unroll
     for (int dt = 0; dt < DT; ++dt) {
       const int d = v0 + dt * 8 + (lane & 3) * 2;
-      if (d < p.dv)
-        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
+      if (d >= p.dv) continue;
+      if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + at + d) = make_float2(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
+      else *reinterpret_cast<__nv_bfloat162*>(p.out + at + d) = __floats2bfloat162_rn(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
     }
   }
 }
@@ -376,7 +386,7 @@ __global__ void attn_flex_merge_kernel(const FlexParams p) {
     if (threadIdx.x == 0) s_inv = L > 0.f ? 1.f / L : 0.f;
   }
   __syncthreads();
-  bf16* dst = p.out + (size_t)(item.row0 + tok) * p.out_stride + (size_t)head * p.dv;
+  const size_t at = (size_t)(item.row0 + tok) * p.out_stride + (size_t)head * p.dv;
   for (int d = threadIdx.x; d < p.dv; d += blockDim.x) {
     float acc = 0.f;
     for (int s0 = 0; s0 < p.nsplit; s0 += 8) {            // eight loads in flight; shares without keys hold nothing
@@ -387,7 +397,8 @@ __global__ void attn_flex_merge_kernel(const FlexParams p) {
 #pragma unroll
       for (int u = 0; u < 8; ++u) acc = fmaf(v[u], s0 + u < p.nsplit ? w[s0 + u] : 0.f, acc);
     }
-    dst[d] = __float2bfloat16_rn(acc * s_inv);
+    if (p.out_f32) p.out_f32[at + d] = acc * s_inv;
+    else p.out[at + d] = __float2bfloat16_rn(acc * s_inv);
   }
 }
 
@@ -428,15 +439,20 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
                            const int* block_table, int table_width, const int* items, int num_items, void* out,
                            long long out_stride, int num_pages, int page_size, int num_seqs, int H, int KV, int dk,
                            int dv, float scale, int window, const float* dist_bias, int nd, const float* sink,
-                           int nsplit, float* scratch, int max_rows, int* status, cudaStream_t stream) {
+                           int nsplit, float* scratch, int max_rows, float softcap, int v_share, int out_is_f32,
+                           int* status, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (!si_attn_flex_ok(H, KV, dk, dv, v_cache != nullptr) || nsplit < 1 || nsplit > 64 || (nsplit > 1 && !scratch)) return -2;
+  if (v_share < 1 || KV % v_share || (v_share > 1 && !v_cache) || softcap < 0.f) return -2;
   FlexParams p;
   p.q = (const bf16*)q; p.q_stride = q_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.table_width = table_width;
   p.items = (const AttnItem*)items; p.num_items = num_items;
-  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.out = out_is_f32 ? nullptr : (bf16*)out; p.out_stride = out_stride;
+  p.out_f32 = out_is_f32 ? (float*)out : nullptr;
+  p.cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+  p.v_share = v_share;
   p.dist_bias = dist_bias; p.nd = nd; p.sink = sink;
   p.num_pages = num_pages; p.page_size = page_size; p.num_seqs = num_seqs;
   p.H = H; p.KV = KV; p.G = H / KV; p.Gb = flex_heads_per_block(p.G); p.hparts = p.G / p.Gb;

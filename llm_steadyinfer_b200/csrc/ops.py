@@ -1099,25 +1099,27 @@ def attn_flex_scratch_floats(num_items: int, H: int, KV: int, dv: int, nsplit: i
 
 def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_seqs: int, H: int, KV: int, dk: int,
               dv: int, scale: float, window: int = 0, dist_bias=None, sink=None, nsplit: int = 1, scratch=None,
-              status=None, max_rows: int = 0) -> None:
+              status=None, max_rows: int = 0, softcap: float = 0.0, v_share: int = 1) -> None:
     """``attention_general`` on the tensor cores for bfloat16. ``items``: int32 [n, 4] rows (sequence, first row,
     tokens, first position) of at most ``attn_flex_tokens`` tokens. ``nsplit`` > 1 cuts every item's keys into that
     many shares (decode rows over long contexts); ``scratch`` then holds ``attn_flex_scratch_floats`` floats.
     ``max_rows``: the most rows (tokens x query heads of a key head served together) of any item when the caller knows it
-    (0: unknown); at most 16 rows over keys that are their own values let a block's warps take a value slice each."""
+    (0: unknown); at most 16 rows over keys that are their own values let a block's warps take a value slice each.
+    ``softcap``, ``v_share`` as in ``attention_general``; ``out`` may be fp32."""
     _cuda(q, k_cache, v_cache, block_table, items, out, dist_bias, sink, scratch, status)
     _i32(block_table, "block_table"); _i32(items, "items")
-    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    _need(v_share >= 1 and KV % v_share == 0 and (v_share == 1 or v_cache is not None), "attn_flex: v_share")
+    _need(q.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32) and k_cache.dtype == torch.bfloat16
           and (v_cache is None or v_cache.dtype == torch.bfloat16), "attn_flex: bfloat16 tensors only")
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == H * dk and out.shape[1] == H * dv,
           "attn_flex: q must be [T, H*dk], out [T, H*dv]")
     _need(tuple(k_cache.shape[1:]) == (KV, page_size, dk) and k_cache.is_contiguous(), "attn_flex: keys must be [pages, KV, page_size, dk]")
     if v_cache is not None:
-        _need(tuple(v_cache.shape) == (k_cache.shape[0], KV, page_size, dv) and v_cache.is_contiguous(),
-              "attn_flex: values must be [pages, KV, page_size, dv]")
+        _need(tuple(v_cache.shape) == (k_cache.shape[0], KV // v_share, page_size, dv) and v_cache.is_contiguous(),
+              "attn_flex: values must be [pages, KV / v_share, page_size, dv]")
     _need(items.dim() == 2 and items.shape[1] == 4, "attn_flex: items must be int32 [n, 4]")
     _need(q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and k_cache.data_ptr() % 16 == 0
-          and (v_cache is None or v_cache.data_ptr() % 16 == 0) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0,
+          and (v_cache is None or v_cache.data_ptr() % 16 == 0) and out.data_ptr() % 8 == 0 and out.stride(0) % 2 == 0,
           "attn_flex: q and the caches must be 16-byte aligned")
     nd = 0
     if dist_bias is not None:
@@ -1131,11 +1133,11 @@ def attn_flex(q, k_cache, v_cache, block_table, items, out, page_size: int, num_
               f"attn_flex: scratch must hold {need} floats")
     f = _fn("attention_flex", "si_attn_flex",
             [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_f, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p])
     _check(f(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(items),
              items.shape[0], _ptr(out), out.stride(0), k_cache.shape[0], page_size, num_seqs, H, KV, dk, dv,
-             float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), int(max_rows), _ptr(status),
-             _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
+             float(scale), int(window or 0), _ptr(dist_bias), nd, _ptr(sink), int(nsplit), _ptr(scratch), int(max_rows),
+             float(softcap or 0.0), int(v_share), 1 if out.dtype == torch.float32 else 0, _ptr(status), _stream()), f"attn_flex(heads={H}, kv_heads={KV}, dk={dk}, dv={dv})", kernels=2 if nsplit > 1 else 1)
 
 
 # ---- one small matrix per head (decode rows) -----------------------------------------------------------------

@@ -23,9 +23,11 @@ import torch
 
 from ..csrc import ops
 from .base import CacheNeed, Mixer, register_mixer
+from . import flex_plan
 from .linear import linear
 
 MAPS = 2
+USE_TENSOR_CORES = True      # bf16 only; False sends bf16 through the plain kernel as well
 
 
 class DiffAttention(Mixer):
@@ -98,8 +100,18 @@ class DiffAttention(Mixer):
         return self.w_in if self.dtype == torch.bfloat16 and rows <= ops.SKINNY_MAX_ROWS else None
 
     def kernel_files(self, page_size):
-        return ("qk_prepare", "attention_general") + (("gemm_f32",) if self.dtype == torch.float32
-                                                      else ("gemm_skinny", "gemm_rows", "gemm_tc05"))
+        if self.dtype == torch.float32:
+            return ("qk_prepare", "attention_general", "gemm_f32")
+        return ("qk_prepare", "attention_flex" if self.uses_flex() else "attention_general", "gemm_skinny", "gemm_rows", "gemm_tc05")
+
+    def uses_flex(self) -> bool:
+        """The maps on the tensor cores: bfloat16 and sizes in multiples of 8."""
+        return (self.dtype == torch.bfloat16 and USE_TENSOR_CORES
+                and ops.attn_flex_ok(self.H * MAPS, self.G * MAPS, self.dk, self.dv, True))
+
+    def prepare(self, ctx, cache):
+        if self.uses_flex() and cache.k is not None:
+            flex_plan.plan(ctx, self.device, self.H * MAPS, self.G * MAPS, self.dk, self.dv, True, self.window)
 
     def forward(self, x, ctx, cache):
         T = x.shape[0]
@@ -125,6 +137,12 @@ class DiffAttention(Mixer):
 
     def attend(self, q, cache, ctx, maps):
         """Both maps of every head as 2 H query heads over 2 G key heads; neighbouring key heads share a value head."""
+        if self.uses_flex():
+            H, G = self.H * MAPS, self.G * MAPS
+            flex_plan.attend(flex_plan.plan(ctx, self.device, H, G, self.dk, self.dv, True, self.window), q, cache.k, cache.v,
+                             cache.block_table, maps, cache.page_size, ctx.seq_slots, H, G, self.dk, self.dv, self.scale,
+                             self.window, status=ctx.status, softcap=self.softcap, v_share=MAPS)
+            return
         ops.attention_general(q, cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.positions, maps, cache.page_size,
                               ctx.seq_slots, self.H * MAPS, self.G * MAPS, self.dk, self.dv, self.scale, self.window or 0,
                               status=ctx.status, softcap=self.softcap, v_share=MAPS)

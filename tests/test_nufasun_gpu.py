@@ -1,0 +1,509 @@
+"""Nufasun on the GPU against the plain implementation (tests/plain_nufasun.py): every mechanism alone, prompts
+against token-by-token decoding, portions down to two tokens, unequal batches with pages and slots used again, keys
+far away, at page borders and at both sides of a window's edge, the first tokens, long decoding, other sizes, and
+greedy generation through the entry point. Weights come from tests/nufasun_configs.py, which makes them so that a
+lost key, state, map or window edge shows."""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import nufasun_configs as nc
+import plain_nufasun as pn
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+
+# A row's error: root mean square of the difference of the logits (mean taken off) over that of the plain logits.
+# In 32-bit every row is held to the limit. In bfloat16 rounding alone gives a median of 0.02 with single rows several
+# times that (a difference of maps that nearly cancels, then a norm): the limit holds for the median and for all but one
+# row in twenty, and no row may pass four times the limit. What a cut, a batch or a page does wrong shows in 32-bit.
+LIMIT = {torch.float32: 2e-4, torch.bfloat16: 8e-2}
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["fp32", "bf16"]
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("nufasun")
+    return {n: nc.write_folder(os.path.join(str(root), n), cfg, seed=21 + i) for i, (n, cfg) in enumerate(nc.CONFIGS.items())}
+
+
+@pytest.fixture(scope="module")
+def plains(folders):
+    return {n: ru.PlainLogits(d, pn) for n, d in folders.items()}
+
+
+def replayer(folder, name, dtype, max_tokens, max_requests=4):
+    from llm_steadyinfer_b200.engine.replay import Replayer
+    return Replayer(folder, dtype, max_tokens, page_size=nc.PAGE_SIZE[name], max_requests=max_requests)
+
+
+def row_error(row, ref):
+    d = row.to(torch.float64) - ref
+    d = d - d.mean()
+    return (d.pow(2).mean().sqrt() / ref.sub(ref.mean()).pow(2).mean().sqrt()).item()
+
+
+def check(rp, steps, reqs, plain, dtype, what):
+    worst, n, errors = 0.0, 0, []
+    hard = LIMIT[dtype] * (4 if dtype == torch.bfloat16 else 1)
+    for rid, p, row in ru.replay_in_process(rp, steps):
+        e = row_error(row, plain.of(reqs[rid])[p])
+        assert e == e and e <= hard, f"{what}: request {rid!r} position {p}: error {e:.3e} (allowed {hard:.0e})"
+        worst, n = max(worst, e), n + 1
+        errors.append(e)
+    assert n > 0
+    if dtype == torch.bfloat16:
+        errors.sort()
+        over = sum(e > LIMIT[dtype] for e in errors)
+        assert over <= max(1, n // 20), f"{what}: {over} of {n} rows above {LIMIT[dtype]:.0e}"
+        assert errors[n // 2] <= LIMIT[dtype] / 2 or n < 4, f"{what}: median error {errors[n // 2]:.3e}"
+    mgr = rp.runner.manager
+    mgr.check_invariant()
+    assert not mgr.requests
+    assert all(mgr.free_pages(g) == mgr.groups[g].pool.num_pages for g in range(len(mgr.groups)))
+    return worst
+
+
+def requests_of(name, lengths, seed=0):
+    vocab = nc.CONFIGS[name]["vocab"]
+    return {f"q{i}": ru.random_tokens(vocab, n, 1000 * seed + i) for i, n in enumerate(lengths)}
+
+
+# ---- each mechanism alone, and the layers of a whole model one by one ------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("name", ["attention", "delta", "mlp", "loop"])
+def test_each_mechanism_alone(folders, plains, name, dtype):
+    """One-layer models: the logits whole and token by token (the attention's window of 11 keys is passed many times)."""
+    reqs = requests_of(name, [1, 2, 37, 90])
+    for mode, steps in (("whole", ru.trace_whole(reqs)), ("tail", ru.trace_tail(reqs, tail=30))):
+        rp = replayer(folders[name], name, dtype, 128)
+        check(rp, steps, reqs, plains[name], dtype, f"{name}/{mode}")
+
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+def test_layers_one_by_one_in_32_bit(folders, name):
+    """The residual stream after every layer run against the plain one (a looped layer counted each time)."""
+    toks = ru.random_tokens(nc.CONFIGS[name]["vocab"], 45, 5)
+    cfg, w = pn.read_model_folder(folders[name])
+    _, want = pn.forward(cfg, w, toks, return_layers=True)
+    rp = replayer(folders[name], name, torch.float32, 64)
+    got = {}
+    rp.runner.model.hook_layers(lambda run, resid: got.__setitem__(run, resid.double().cpu()))
+    rp.run_step([{"id": "a", "tokens": toks, "want": [len(toks) - 1]}], end=["a"])
+    runs = pn.run_order(cfg)
+    assert sorted(got) == list(range(len(runs))) and want.shape[0] == len(runs)
+    for run, (layer, _, _) in enumerate(runs):
+        scale = want[run].abs().max().item()
+        diff = (got[run] - want[run]).abs().max().item()
+        assert diff <= 5e-5 * scale, f"{name}: run {run} (layer {layer}, {cfg['layers'][layer]['type']}) differs by {diff:.2e} of {scale:.1f}"
+
+
+# ---- schedules ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_schedules(folders, plains, name, dtype, mode):
+    reqs = requests_of(name, [1, 3, 19, 64, 65, 130, 201], seed=1)
+    longest = ru.round64(max(len(t) for t in reqs.values()))
+    if mode == "whole":
+        steps, max_tokens = ru.trace_whole(reqs), longest
+    elif mode == "tail":
+        steps, max_tokens = ru.trace_tail(reqs, tail=40), longest
+    elif mode == "portions":
+        steps, max_tokens = ru.trace_portions(reqs, sizes=(2, 17, 3, 2, 31, 5, 64, 2, 9, 1, 40)), longest
+    else:
+        max_tokens = longest + 128                       # two or three live at a time: pages and slots come again
+        steps = ru.trace_mixed(reqs, max_tokens, seed=3, max_live=3)
+    rp = replayer(folders[name], name, dtype, max_tokens, max_requests=3)
+    worst = check(rp, steps, reqs, plains[name], dtype, f"{name}/{mode}")
+    print(f"{name} {mode} {dtype}: worst row error {worst:.2e}")
+
+
+def test_batch_equals_alone_and_slots_come_again(folders, plains):
+    """Unequal requests in one batch against each alone, with two state slots for five requests: every slot and page is
+    used again, and what the request before left there (recurrent state, convolution inputs, keys) must not show."""
+    name, dtype = "mixed_a", torch.float32
+    reqs = requests_of(name, [70, 9, 33, 2, 51], seed=2)
+    steps = ru.trace_mixed(reqs, 192, seed=9, max_live=2, prompt_frac=0.5)
+    rp = replayer(folders[name], name, dtype, 192, max_requests=2)
+    check(rp, steps, reqs, plains[name], dtype, "two slots")
+    again = dict(reversed(list(reqs.items())))
+    check(rp, ru.trace_mixed(again, 192, seed=10, max_live=2, prompt_frac=0.3), again, plains[name], dtype, "two slots again")
+
+
+def test_long_decoding(folders, plains):
+    """A short prompt, then 300 tokens one by one, across many page borders, with every window passing over decoded
+    tokens only; the recurrent state is carried 300 times."""
+    name = "mixed_a"
+    reqs = requests_of(name, [310], seed=3)
+    for dtype in DTYPES:
+        rp = replayer(folders[name], name, dtype, 320)
+        check(rp, ru.trace_tail(reqs, tail=300), reqs, plains[name], dtype, "long decoding")
+
+
+def test_first_tokens(folders, plains):
+    """Positions 0, 1, 2 alone and as the start of portions: the convolution's zeros before the sequence, a state that
+    starts at zero, a softmax over one key, a rotation by angle zero."""
+    name = "mixed_b"
+    reqs = requests_of(name, [1, 2, 3, 5], seed=4)
+    for dtype in DTYPES:
+        for sizes in ((1,), (2, 1), (1, 2)):
+            rp = replayer(folders[name], name, dtype, 64)
+            check(rp, ru.trace_portions(reqs, sizes=sizes), reqs, plains[name], dtype, f"first tokens {sizes}")
+
+
+def test_a_token_far_back_reaches_through_the_state(tmp_path):
+    """A delta layer whose decay is almost one: what token 3 wrote is read 400 tokens later. The logits with another
+    token at place 3 must differ in the plain implementation (a hundred times the 32-bit limit), and the engine must
+    follow it, cut in portions."""
+    cfg = nc._model(120, 64, 1e-5, [nc._layer("delta", nc._delta(4, 2, 64, 16, 2), ff=48)])
+
+    def slow_decay(t):
+        t["l0.mix.dt_bias"][:] = -9.0                      # decay about exp(-1e-4) a token
+        t["l0.mix.a"][:] = 0.0
+
+    folder = nc.write_folder(str(tmp_path / "far"), cfg, 5, change=slow_decay)
+    plain = ru.PlainLogits(folder, pn)
+    a = ru.random_tokens(120, 420, 77)
+    b = list(a)
+    b[3] = (a[3] + 17) % 120
+    la, lb = plain.of(a)[-1], plain.of(b)[-1]
+    assert row_error(la, lb) > 20 * LIMIT[torch.float32], "the test's weights do not carry the far token"
+    for dtype in DTYPES:
+        rp = replayer(folder, "delta", dtype, 448)
+        reqs = {"a": a, "b": b}
+        check(rp, ru.trace_portions(reqs, sizes=(64, 2, 100, 31, 1)), reqs, plain, dtype, "far token")
+
+
+# ---- kernels with inputs that make one key count -----------------------------------------------------------
+
+def _paged(rows, page_size, perm_seed):
+    """rows [n, heads, d] into a shuffled page pool; returns (cache [pages, heads, page_size, d], table [1, blocks])."""
+    n, KV, d = rows.shape
+    blocks = -(-n // page_size)
+    g = torch.Generator().manual_seed(perm_seed)
+    pages = torch.randperm(blocks + 3, generator=g)[:blocks]
+    cache = torch.zeros(blocks + 3, KV, page_size, d, dtype=rows.dtype)
+    for j in range(n):
+        cache[pages[j // page_size], :, j % page_size] = rows[j]
+    return cache, pages.to(torch.int32).view(1, -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("window,softcap", [(37, 8.0), (64, 0.0), (None, 25.0)])
+def test_attention_maps_window_edges_and_far_keys(window, softcap, dtype):
+    """Two maps a head over shared values, with queries built so that one key carries nearly all the weight: the key
+    just inside the window, the one just outside it (which must not count), keys at page borders, and a key far back.
+    Rows are run as a prompt (all at once) and once more one by one."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(3)
+    n, H, G, dk, dv, ps, M = 330, 4, 2, 24, 40, 16, 2
+    ratio = H // G
+    k = torch.randn(n, G, M, dk) * 0.3
+    v = torch.randn(n, G, dv)
+    q = torch.randn(n, H, M, dk) * 0.3
+    w = window or n
+    dists = sorted({0, 1, w - 2, w - 1, w, w + 1, 15, 16, 17, 31, 32, 33, 250, 300} & set(range(n)))
+    for e, dist in enumerate(dists):                      # query i looks hard at the key `dist` back, in both maps
+        i = n - 1 - e
+        if i - dist < 0:
+            continue
+        k[i - dist] = k[i - dist] / k[i - dist].norm(dim=-1, keepdim=True) * 6.0
+        for h in range(H):
+            q[i, h] = k[i - dist, h // ratio] * (1.5 if h % 2 else 1.0)
+    q, k, v = (t.to(dtype).float() for t in (q, k, v))
+    scale = 0.5
+    ref = torch.zeros(n, H, M, dv, dtype=torch.float64)
+    for h in range(H):
+        for m in range(M):
+            ref[:, h, m] = pn.windowed_softmax_attention(q[:, h, m].double(), k[:, h // ratio, m].double(), v[:, h // ratio].double(),
+                                                         scale, softcap, window)
+    # what the engine's kernels see: queries ordered [key head][map][head of the group], 2 G key heads, G value heads
+    qd = q.view(n, G, ratio, M, dk).permute(0, 1, 3, 2, 4).reshape(n, H * M * dk).to(dtype).to(DEV)
+    kc, table = _paged(k.reshape(n, G * M, dk).to(dtype), ps, 3)
+    vc = _paged(v.to(dtype), ps, 3)[0]
+    seqs, pos = torch.zeros(n, dtype=torch.int32, device=DEV), torch.arange(n, dtype=torch.int32, device=DEV)
+    want = ref.view(n, G, ratio, M, dv).permute(0, 1, 3, 2, 4).reshape(n, H * M * dv)
+    limit = 1e-4 if dtype == torch.float32 else 3e-2
+    out = torch.zeros(n, H * M * dv, dtype=torch.float32, device=DEV)
+    ops.attention_general(qd, kc.to(DEV), vc.to(DEV), table.to(DEV), seqs, pos, out, ps, 1, H * M, G * M, dk, dv, scale,
+                          window or 0, softcap=softcap, v_share=M)
+    diff = (out.double().cpu() - want).abs().max().item()
+    assert diff <= limit, f"prompt rows differ by {diff:.2e}"
+    # the key just outside the window would have dominated: the plain result with a window one longer differs clearly
+    if window:
+        i = n - 1 - dists.index(window)
+        wider = pn.windowed_softmax_attention(q[:, 0, 0].double(), k[:, 0, 0].double(), v[:, 0].double(), scale, softcap, window + 1)
+        assert (wider[i] - ref[i, 0, 0]).abs().max().item() > 0.1
+    last = 40
+    one = torch.zeros(last, H * M * dv, dtype=torch.float32, device=DEV)
+    for r in range(n - last, n):                          # single rows, as decoding brings them
+        ops.attention_general(qd[r:r + 1], kc.to(DEV), vc.to(DEV), table.to(DEV), seqs[:1], pos[r:r + 1], one[r - n + last:r - n + last + 1],
+                              ps, 1, H * M, G * M, dk, dv, scale, window or 0, softcap=softcap, v_share=M)
+    diff = (one.double().cpu() - want[n - last:]).abs().max().item()
+    assert diff <= limit, f"single rows differ by {diff:.2e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("NQ,NK,NV,dk,dv,rd,interleaved,maps", [(8, 4, 2, 24, 40, 8, True, 2), (6, 2, 2, 32, 16, 32, False, 1),
+                                                                 (4, 4, 2, 10, 6, 6, True, 2), (3, 1, 1, 64, 64, 0, True, 1)])
+def test_query_key_preparation(NQ, NK, NV, dk, dv, rd, interleaved, maps, dtype):
+    """Norm, rotation (both pairings), the order of the prepared queries and the stores into the pages."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(NQ * dk)
+    T, ps, eps, base = 37, 8, 1e-5, 5000.0
+    width = (NQ + NK) * dk + NV * dv + 5
+    rows = torch.randn(T, width).to(dtype)
+    qw, kw = 1 + 0.3 * torch.randn(dk), 1 + 0.3 * torch.randn(dk)
+    positions = torch.arange(100, 100 + T)
+    inv_freq = (base ** (-torch.arange(0, rd, 2, dtype=torch.float64) / rd)).float() if rd else None
+    x = rows.double()
+    qn = pn.rms_norm(x[:, :NQ * dk].view(T, NQ, dk), qw.double(), eps)
+    kn = pn.rms_norm(x[:, NQ * dk:(NQ + NK) * dk].view(T, NK, dk), kw.double(), eps)
+    if rd:
+        if interleaved:
+            qn, kn = pn.rotate_pairs(qn, positions, base, rd), pn.rotate_pairs(kn, positions, base, rd)
+        else:                                             # pairs (i, i + rd/2)
+            def halves(t):
+                f = base ** (-2.0 * torch.arange(rd // 2, dtype=torch.float64) / rd)
+                a = positions.double()[:, None, None] * f
+                u, v = t[..., :rd // 2], t[..., rd // 2:rd]
+                return torch.cat([u * a.cos() - v * a.sin(), v * a.cos() + u * a.sin(), t[..., rd:]], -1)
+            qn, kn = halves(qn), halves(kn)
+    ratio = NQ // NK
+    if maps > 1:                                          # [head][map] -> [key head][map][head of the group]
+        hk = NK // maps
+        qn = qn.view(T, hk, ratio, maps, dk).permute(0, 1, 3, 2, 4).reshape(T, NQ, dk)
+    blocks = -(-(100 + T) // ps)
+    table = torch.randperm(blocks + 2)[:blocks].to(torch.int32).view(1, -1)
+    kc = torch.zeros(blocks + 2, NK, ps, dk, dtype=dtype, device=DEV)
+    vc = torch.zeros(blocks + 2, NV, ps, dv, dtype=dtype, device=DEV)
+    q_out = torch.zeros(T, NQ * dk, dtype=dtype, device=DEV)
+    rd_dev = rows.to(DEV)
+    ops.qk_prepare(rd_dev, qw.to(DEV), kw.to(DEV), eps, inv_freq.to(DEV) if rd else None, rd, interleaved, positions.to(torch.int32).to(DEV),
+                   torch.zeros(T, dtype=torch.int32, device=DEV), table.to(DEV), kc, vc, ps, 1, NQ, NK, NV, dk, dv, q_out=q_out, maps=maps)
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert (q_out.double().cpu().view(T, NQ, dk) - qn).abs().max().item() <= tol * qn.abs().max().item()
+    for t in range(T):
+        p = 100 + t
+        page = int(table[0, p // ps])
+        assert (kc[page, :, p % ps].double().cpu() - kn[t]).abs().max().item() <= tol * kn.abs().max().item()
+        assert torch.equal(vc[page, :, p % ps].cpu().view(-1), rows[t, (NQ + NK) * dk:(NQ + NK) * dk + NV * dv])
+    assert torch.equal(rd_dev.cpu(), rows)                # with a q_out of their own the rows stay as they were
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_maps_combined(dtype):
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(4)
+    T, H, ratio, dv, lam, eps, post = 19, 6, 3, 20, 0.83, 1e-5, 0.7
+    a = torch.randn(T, H // ratio, 2, ratio, dv)
+    gate = torch.randn(T, H + 3).to(dtype)
+    want = torch.zeros(T, H, dv, dtype=torch.float64)
+    for h in range(H):
+        o = a[:, h // ratio, 0, h % ratio].double() - lam * a[:, h // ratio, 1, h % ratio].double()
+        want[:, h] = pn.rms_norm(o, None, eps) * post * torch.sigmoid(gate[:, 1 + h].double())[:, None]
+    out = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
+    ops.diff_combine(a.reshape(T, -1).to(DEV), gate.to(DEV)[:, 1:1 + H], out, H, dv, ratio, lam, eps, post)
+    assert (out.double().cpu().view(T, H, dv) - want).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 24, 16, 4), (3, 3, 64, 128, 2), (2, 1, 5, 9, 1), (8, 2, 128, 64, 3), (2, 2, 160, 24, 5)])
+def test_delta_rule_kernels_in_portions(H, G, dk, dv, taps):
+    """Convolution, preparation, recurrence and the read-out's norm over one sequence cut into portions (2, 1, 17, ...)
+    beside a second sequence, against the plain functions on the whole sequence; the slot starts with another request's
+    leavings."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(H * 100 + dk)
+    T = 84
+    C = 2 * G * dk + H * dv
+    u = torch.randn(T, C + H * dv + 2 * H)                 # [q | k | v | gate | b | a] rows as the projection lays them out
+    conv_w = torch.randn(C, taps) * 0.5
+    a_log, dt_bias = torch.empty(H).uniform_(-1, 1), torch.empty(H).uniform_(-4, -1)
+    norm_w = 1 + 0.1 * torch.randn(dv)
+    x = pn.causal_conv_silu(u[:, :C].double(), conv_w.double())
+    q = pn.unit(x[:, :G * dk].view(T, G, dk)) * dk ** -0.5
+    k = pn.unit(x[:, G * dk:2 * G * dk].view(T, G, dk))
+    v = x[:, 2 * G * dk:].view(T, H, dv)
+    beta = torch.sigmoid(u[:, C + H * dv:C + H * dv + H].double())
+    decay = torch.exp(-torch.exp(a_log.double()) * torch.nn.functional.softplus(u[:, C + H * dv + H:].double() + dt_bias.double()))
+    gate = u[:, C:C + H * dv].double().view(T, H, dv)
+    want = torch.zeros(T, H, dv, dtype=torch.float64)
+    for h in range(H):
+        g = h // (H // G)
+        o = pn.delta_rule_head(q[:, g], k[:, g], v[:, h], beta[:, h], decay[:, h])
+        want[:, h] = pn.rms_norm(o, norm_w.double(), 1e-5) * gate[:, h] * torch.sigmoid(gate[:, h])
+    conv_off = H * dk * dv
+    state = torch.randn(3, conv_off + (taps - 1) * C, device=DEV)          # stale contents
+    got = torch.zeros(T, H * dv, device=DEV)
+    ud = u.to(DEV)
+    other = torch.randn(40, u.shape[1], device=DEV)
+    zero_b = torch.zeros(C, device=DEV)
+    p = po = 0
+    for n in (2, 1, 17, 3, 30, 1, 1, 29):
+        no = min(5, 40 - po)
+        rows = torch.cat([other[po:po + no], ud[p:p + n]])                    # the other sequence first, in slot 2
+        R = rows.shape[0]
+        ints = lambda *vals: torch.tensor(vals, dtype=torch.int32, device=DEV)
+        positions = torch.cat([torch.arange(po, po + no), torch.arange(p, p + n)]).to(torch.int32).to(DEV)
+        row_seq = torch.tensor([0] * no + [1] * n, dtype=torch.int32, device=DEV)
+        q_start, ctx_len, slots = ints(0, no, R), ints(po + no, p + n), ints(2, 1)
+        xc = torch.zeros(R, C, device=DEV)
+        ops.causal_conv(rows[:, :C], conv_w.to(DEV), zero_b, state, conv_off, xc, positions, row_seq, q_start, ctx_len, slots, 2)
+        bg = torch.zeros(R, 2 * H, device=DEV)
+        ops.delta_prepare(xc, rows, C + H * dv, C + H * dv + H, a_log.to(DEV), dt_bias.to(DEV), bg, G, H, dk, dk ** -0.5)
+        y = torch.zeros(R, H * dv, device=DEV)
+        ops.delta_scan(xc, bg, state, y, q_start, ctx_len, slots, 2, G, H, dk, dv)
+        go = torch.zeros(R, H * dv, device=DEV)
+        ops.head_norm_gate(y, rows[:, C:C + H * dv], norm_w.to(DEV), go, H, dv, 1e-5)
+        got[p:p + n] = go[no:]
+        p, po = p + n, po + no
+    assert p == T
+    diff = (got.double().cpu().view(T, H, dv) - want).abs().max().item()
+    assert diff <= 2e-4 * max(1.0, want.abs().max().item()), f"differs by {diff:.2e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("width", [70, 192, 2048])
+def test_the_add_in_its_general_form(width, dtype):
+    """A normalised delta with a bias, the embedding's output and a vector join the stream; the stream's own norm behind
+    it; and the same for chosen rows only, which leaves the stream as it is."""
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(width)
+    T, eps, deps = 11, 1e-5, 2e-6
+    resid, delta = torch.randn(T, width) * 3, torch.randn(T, width).to(dtype)
+    bias, extra, vec = torch.randn(width), torch.randn(T, width), torch.randn(width)
+    w, dw = (1 + 0.2 * torch.randn(width)).to(dtype), (1 + 0.2 * torch.randn(width)).to(dtype)
+    d = pn.rms_norm(delta.double() + bias.double(), dw.double(), deps)
+    h = resid.double() + d + extra.double() + vec.double()
+    want = pn.rms_norm(h, w.double(), eps)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    r = resid.to(DEV).clone()
+    out = torch.zeros(T, width, dtype=dtype, device=DEV)
+    ops.add_norm(r, delta.to(DEV), w.to(DEV), eps, out, delta_weight=dw.to(DEV), delta_eps=deps, delta_bias=bias.to(DEV),
+                 extra=extra.to(DEV), vec=vec.to(DEV))
+    assert (r.double().cpu() - h).abs().max().item() <= 1e-5 * h.abs().max().item() + (0 if dtype == torch.float32 else 2e-2)
+    assert (out.double().cpu() - want).abs().max().item() <= tol * want.abs().max().item()
+    r2 = resid.to(DEV).clone()
+    ops.add_norm(r2, delta.to(DEV), delta_weight=dw.to(DEV), delta_eps=deps, delta_bias=bias.to(DEV), extra=extra.to(DEV), vec=vec.to(DEV))
+    assert torch.equal(r2, r)                              # without an output the stream gets the same sums
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32, device=DEV)
+    r3 = resid.to(DEV).clone()
+    some = torch.zeros(3, width, dtype=dtype, device=DEV)
+    ops.add_norm(r3, delta.to(DEV), w.to(DEV), eps, some, rows=rows, delta_weight=dw.to(DEV), delta_eps=deps, delta_bias=bias.to(DEV))
+    assert torch.equal(r3.cpu(), resid)
+    h3 = resid.double() + d
+    assert (some.double().cpu() - pn.rms_norm(h3, w.double(), eps)[[7, 0, 3]]).abs().max().item() <= tol * want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("F,group", [(24, 8), (10, 10), (96, 8)])
+def test_limited_gated_activation_on_both_sides_of_the_limit(F, group, dtype):
+    from llm_steadyinfer_b200.csrc import ops
+    torch.manual_seed(F)
+    T, limit, alpha = 9, 0.8, 1.702
+    g, u = (torch.randn(T, F) * 1.5).to(dtype), (torch.randn(T, F) * 1.5).to(dtype)
+    bg, bu = torch.randn(F) * 0.3, torch.randn(F) * 0.3
+    gg = torch.clamp(g.double() + bg.double(), max=limit)
+    uu = torch.clamp(u.double() + bu.double(), -limit, limit)
+    want = gg * torch.sigmoid(alpha * gg) * (uu + 1)
+    assert (g.double() + bg.double() > limit).any() and (u.double() + bu.double() < -limit).any()
+    n = F // group
+    stack = lambda a, b: torch.stack([a.view(*a.shape[:-1], n, group), b.view(*b.shape[:-1], n, group)], -2).reshape(*a.shape[:-1], 2 * F)
+    out = torch.zeros(T, F, dtype=dtype, device=DEV)
+    ops.glu_limited(stack(g, u).contiguous().to(DEV), stack(bg, bu).contiguous().to(DEV), out, group, limit, alpha)
+    assert (out.double().cpu() - want).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+# ---- the entry point ----------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", ["mixed_a", "mixed_b", "odd"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    """Greedy tokens through LLM (scheduler, sampler, graphs and steps launched ahead) equal the plain implementation's
+    in 32-bit; bfloat16 runs and mostly agrees."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    cfg, w = pn.read_model_folder(folders[name])
+    prompts = [ru.random_tokens(cfg["vocab"], n, 50 + n) for n in (5, 23, 1, 40)]
+    want = [pn.greedy(cfg, w, p, 12) for p in prompts]
+    for dtype in ("float32", "bfloat16"):
+        for graphs in (True, False):
+            llm = LLM(folders[name], dtype=dtype, max_batch=3, max_seq_len=64, max_gen_len=12, block_size=nc.PAGE_SIZE[name],
+                      max_num_batched_tokens=32, use_cuda_graph=graphs, async_decode=graphs)
+            got = [g.token_ids for g in llm.generate(prompts, SamplingParams(ignore_eos=True))]
+            if dtype == "float32":
+                assert got == want, f"{name} graphs={graphs}: {got} != {want}"
+            else:
+                same = sum(a == b for g, x in zip(got, want) for a, b in zip(g, x))
+                assert same >= 24, f"{name} bf16: only {same} of 48 tokens agree"
+            if graphs:
+                assert llm.runner.graphs_available() and llm.stats["graph_steps"] > 0
+
+
+def test_preemption_recomputes_state_from_the_start(folders):
+    """A pool too small for all requests: some are cut back and computed again; with per-request state and windows
+    nothing of a cut request can be kept, and the tokens still equal the plain implementation's."""
+    from llm_steadyinfer_b200 import LLM, SamplingParams
+    name = "mixed_a"
+    cfg, w = pn.read_model_folder(folders[name])
+    prompts = [ru.random_tokens(cfg["vocab"], n, 90 + n) for n in (30, 28, 26)]
+    want = [pn.greedy(cfg, w, p, 20) for p in prompts]
+    llm = LLM(folders[name], dtype="float32", max_batch=3, max_seq_len=64, max_gen_len=20, block_size=8, num_blocks=14,
+              max_num_batched_tokens=64)
+    res = llm.generate(prompts, SamplingParams(ignore_eos=True))
+    assert [r.token_ids for r in res] == want
+    assert sum(r.num_preemptions for r in res) > 0
+
+
+def test_trace_program(folders, plains, tmp_path):
+    """bin/trace_run as a program on a mixed trace."""
+    name = "mixed_a"
+    reqs = requests_of(name, [40, 7, 90], seed=6)
+    steps = ru.trace_mixed(reqs, 256, seed=1, max_live=3)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders[name], "--dtype", "float32",
+                           "--out", str(out), "--max-tokens", "256", "--page-size", str(nc.PAGE_SIZE[name])],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    pos, vocab = {}, nc.CONFIGS[name]["vocab"]
+    for rec in steps:
+        wanted = sum(len(e["want"]) for e in rec["entries"])
+        rows = None
+        if wanted:
+            rows = torch.from_file(str(out / f"{rec['step']}.f32"), size=wanted * vocab, dtype=torch.float32).view(wanted, vocab)
+        r = 0
+        for e in rec["entries"]:
+            base = pos.get(e["id"], 0)
+            for wpos in e["want"]:
+                assert row_error(rows[r], plains[name].of(reqs[e["id"]])[base + wpos]) <= LIMIT[torch.float32]
+                r += 1
+            pos[e["id"]] = base + len(e["tokens"])
+
+
+def test_command_line_serves_the_design(folders, tmp_path):
+    """The serving program on a Nufasun folder: requests of random lengths arriving over time, sampling, a pool that is
+    used again; and once more on random weights drawn from a configuration file."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "m.json"
+    common = ["--num-requests", "12", "--max-batch", "4", "--max-gen", "10", "--prompt-len-dist", "lognormal:30,0.7,2,90",
+              "--output-len-dist", "lognormal:6,0.5,1,10", "--request-rate", "300", "--temperature", "0.8", "--top-p", "0.9",
+              "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "60", "--max-num-batched-tokens", "40",
+              "--max-model-len", "128", "--output-json", str(out)]
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(nc.MIXED_B))
+    for source in (["--checkpoint", folders["mixed_a"]], ["--model-config", str(cfg_file)]):
+        proc = subprocess.run([sys.executable, os.path.join(root, "bin", "offline_batch_benchmark"), *source, *common],
+                              capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        m = json.loads(out.read_text())[0]
+        assert m["completed"] == 12 and m["rejected"] == 0 and m["output_tokens"] > 12 and m["output_tps"] > 0

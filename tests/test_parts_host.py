@@ -62,10 +62,10 @@ def test_a_norm_is_given_the_hint_only_if_it_says_it_takes_one():
 def test_block_arrangements_are_a_registry():
     from llm_steadyinfer_b200.parts import arrangement, register_arrangement
     import pytest
-    assert callable(arrangement("pre_norm"))
+    assert callable(arrangement("pre_norm")) and callable(arrangement("sandwich"))
     with pytest.raises(KeyError) as e:
-        arrangement("sandwich")
-    assert "pre_norm" in str(e.value) and "sandwich" in str(e.value)
+        arrangement("post_norm_only")
+    assert "pre_norm" in str(e.value) and "post_norm_only" in str(e.value)
     calls = []
     register_arrangement("host_test_order", lambda block, resid, delta, ctx, cache: calls.append(block) or "out")
     b = Block(None, None, None, None, "host_test_order")
