@@ -252,7 +252,21 @@ def _llama_twin():
     return d
 
 
-def mivorax_section(args) -> int:
+# ---- the Nufasun design beside the closest existing models ---------------------------------------------------
+_DIFF = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 50.0, "diff": 0.3,
+         "mask": {"size": 4096}, "rot": {"base": 500000.0, "dims": 64}}
+_DELTA = {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}
+
+
+def _nufasun_config():
+    mlp = {"kind": "dense", "ff": MIVORAX_FF, "limit": 7.0}
+    one = [{"type": "attention", "mixer": _DIFF, "mlp": mlp}, {"type": "attention", "mixer": _DIFF, "mlp": mlp},
+           {"type": "delta", "mixer": _DELTA, "mlp": mlp}, {"type": "attention", "mixer": _DIFF, "mlp": mlp}]
+    return {"architecture": "Nufasun", "vocab": MIVORAX_VOCAB, "width": MIVORAX_WIDTH, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 8.0}, "logit_softcap": 30.0, "loop": {"start": 0, "stop": 8, "times": 1}, "layers": one + one}
+
+
+def mivorax_section(args, section="mivorax") -> int:
     """Prefill of 2,048 tokens and decode (batch 8, context 4,096) of an 8-layer Mivorax model (2 latent attention,
     4 attention with distance bias, 2 state-space layers; width 2,048) and of a Llama model of the same width, depth,
     heads and vocabulary; random weights, bf16. Per model: milliseconds per step, tokens/s, and the device time per
@@ -271,7 +285,18 @@ def mivorax_section(args) -> int:
     rand_tokens = lambda n: torch.randint(0, MIVORAX_VOCAB, (n,), generator=gen).tolist()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")        # larger than L2: written between timed steps
     results = {}
-    for name, cfg_d in (("mivorax", _mivorax_config()), ("llama", _llama_twin())):
+    if section == "nufasun":
+        # 8 layers (6 differential attention: 16 heads of two maps of 64 over 4 key/value heads, values of 128, window
+        # 4,096; 2 gated delta rule: 16 heads of 128 x 128 over 8 query/key heads; gated feed-forward 5,632) beside the
+        # Mivorax and Llama models of the same width, depth and vocabulary
+        designs = (("nufasun", _nufasun_config()), ("mivorax", _mivorax_config()), ("llama", _llama_twin()))
+        mixers = {"attention": _DIFF, "delta": _DELTA}
+    else:
+        designs = (("mivorax", _mivorax_config()), ("llama", _llama_twin()))
+        mixers = {"latent": _LATENT, "attention": _BIASED, "state_space": _SSM}
+    for name, cfg_d in designs:
+        if args.only_design and name != args.only_design:
+            continue
         model = Model(config_from_dict(cfg_d), torch.bfloat16, "cuda:0")
         init_random(model, seed=0)
         runner = ModelRunner(model, page_size=PAGE, num_pages=(B * CTX + PT) // PAGE + 8, max_requests=max(B, 2) + 1,
@@ -334,7 +359,7 @@ def mivorax_section(args) -> int:
             torch.cuda.synchronize()
             torch.cuda.cudart().cudaProfilerStop()
             runner.check_status()
-            print(json.dumps({"section": "mivorax", "profiled": name, "prefill_tokens": PT, "decode_batch": B, "decode_context": CTX}))
+            print(json.dumps({"section": section, "profiled": name, "prefill_tokens": PT, "decode_batch": B, "decode_context": CTX}))
             return 0
         dec_ms = timed_each(decode, K)
         with KernelTimes() as kt:
@@ -350,10 +375,10 @@ def mivorax_section(args) -> int:
         del runner, model
         torch.cuda.empty_cache()
     pk, pk_src = peaks()
-    print(json.dumps({"section": "mivorax", "dtype": "bf16", "data": "synthetic: random weights (seed 0), random token ids",
+    print(json.dumps({"section": section, "dtype": "bf16", "data": "synthetic: random weights (seed 0), random token ids",
                       "config": {"width": MIVORAX_WIDTH, "layers": 8, "ff": MIVORAX_FF, "vocab": MIVORAX_VOCAB, "prefill_tokens": PT,
                                  "decode_batch": B, "decode_context": CTX, "page_size": PAGE, "l2": "256 MB written between timed steps",
-                                 "latent": _LATENT, "attention": _BIASED, "state_space": _SSM},
+                                 **mixers},
                       "peaks": pk, "peaks_source": pk_src, "models": results}))
     return 0
 
@@ -386,10 +411,12 @@ def main() -> int:
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed region of --section with cudaProfilerStart/Stop "
                          "(for ncu --profile-from-start off)")
-    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill", "mivorax"],
+    ap.add_argument("--section", default="all", choices=["all", "decode", "prefill", "mivorax", "nufasun"],
                     help="run only the device-timed decode steps or only the prefill (for profiling); 'mivorax': prefill "
                          "and decode of a Mivorax model at layer sizes of a real model beside a Llama model of equal "
-                         "width, with time per kind of kernel (its own JSON line; the default workload is not run)")
+                         "width, with time per kind of kernel (its own JSON line; the default workload is not run); "
+                         "'nufasun': the same for a Nufasun model beside the Mivorax and Llama models")
+    ap.add_argument("--only-design", default=None, help="--section mivorax / nufasun: run this model alone (for profiling)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -398,8 +425,8 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     K, W = args.steps, max(3, args.warmup)
-    if args.section == "mivorax":
-        return mivorax_section(args)
+    if args.section in ("mivorax", "nufasun"):
+        return mivorax_section(args, args.section)
 
     import torch
     from llm_steadyinfer_b200 import LLM, SamplingParams

@@ -24,7 +24,7 @@ struct FlexParams {
   const AttnItem* items; int num_items;
   bf16* out; long long out_stride;
   float* out_f32;           // not null: results go here as fp32 (same strides), not to `out`
-  float cap_log2, scale_over_cap;   // soft limit: cap * log2(e) and scale / cap (cap_log2 0: none)
+  float cap_log2, scale_over_cap;   // soft limit: cap * log2(e) and 2 * log2(e) * scale / cap (cap_log2 0: none)
   int v_share;              // key heads that read one value head
   float* part_o;            // [item][gy][split][64 rows][dv]   (nsplit > 1)
   float* part_ml;           // [item][gy][split][64 rows][2]
@@ -219,7 +219,8 @@ attn_flex_kernel(const FlexParams p) {
           const bool vis = j >= kv_lo && j <= pos && (p.window <= 0 || j > pos - p.window);
           float v = -INFINITY;
           if (vis) {
-            v = p.cap_log2 > 0.f ? p.cap_log2 * tanhf(s[nt][e] * p.scale_over_cap) : s[nt][e] * p.scale_log2;
+            // tanh(y) = 1 - 2 / (exp(2 y) + 1): absolute error of some 1e-7, which is what counts for a score
+            v = p.cap_log2 > 0.f ? p.cap_log2 * (1.f - __fdividef(2.f, exp2f(s[nt][e] * p.scale_over_cap) + 1.f)) : s[nt][e] * p.scale_log2;
             if (p.bias_in_smem) v += Bt[(pos - j - dlo) * p.Gb + ((e < 2) ? hh_lo : hh_hi)];
             else if (p.dist_bias) v += p.dist_bias[(size_t)min(pos - j, p.nd - 1) * p.H + ((e < 2) ? head_lo : head_hi)] * LOG2E;
           }
@@ -451,7 +452,7 @@ SI_EXPORT int si_attn_flex(const void* q, long long q_stride, const void* k_cach
   p.items = (const AttnItem*)items; p.num_items = num_items;
   p.out = out_is_f32 ? nullptr : (bf16*)out; p.out_stride = out_stride;
   p.out_f32 = out_is_f32 ? (float*)out : nullptr;
-  p.cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.scale_over_cap = softcap > 0.f ? 2.f * LOG2E * scale / softcap : 0.f;
   p.v_share = v_share;
   p.dist_bias = dist_bias; p.nd = nd; p.sink = sink;
   p.num_pages = num_pages; p.page_size = page_size; p.num_seqs = num_seqs;

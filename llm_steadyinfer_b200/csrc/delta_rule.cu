@@ -4,16 +4,19 @@
 // so the read-out sees the token's own write. Everything that enters the recurrence is fp32.
 //
 // Two kernels. `delta_prepare` works on all rows at once: it makes q and k unit vectors per head
-// (x / sqrt(sum(x^2) + 1e-6), q also times `q_scale`), beta = sigmoid(b) and g = exp(-exp(A_log) * softplus(a + dt_bias)).
+// (x / sqrt(sum(x^2) + 1e-6), q also times `q_scale`), beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias))
+// and q . k of the prepared vectors.
 // `delta_scan` walks the tokens of every sequence of the step in order. The columns of S are independent of one
-// another, so a block takes (sequence, head, a cut of COLS columns); thread (column j, part p) keeps the rows
-// p, p + NP, p + 2 NP, ... of column j in registers. Per token it forms its parts of k . S[:, j], q . S[:, j] and q . k
-// from the old state, the NP parts of a column (neighbouring lanes) are added with shuffles, and then
+// another, so a block takes (sequence, head, a cut of the columns); thread (column j, part p) keeps RPT neighbouring
+// rows of column j in registers. Per token it forms its parts of k . S[:, j] and q . S[:, j] from the old state (two
+// rows at a time on the packed fp32 instructions, two sums each, so that the chain of dependent additions is short),
+// the NP parts of a column (neighbouring lanes) are added with shuffles, and then
 //   kS = g (k . S_old[:, j]);  u_j = beta (v_j - kS);  o_j = g (q . S_old[:, j]) + (q . k) u_j;  S[:, j] <- g S_old[:, j] + k u_j
-// which is the order above with one pass over the registers for the sums and one for the update. q, k, v, beta and g of
-// CHUNK tokens are staged in shared memory at a time; within a chunk the warps do not wait for one another.
-// A request's state is [heads, dk, dv] fp32 at the start of its slot; a portion that begins at position 0 starts from
-// zero whatever the slot held.
+// which is the order above with one pass over the registers for the sums and one for the update. q, k, v, beta, g and
+// q . k of CHUNK tokens arrive by cp.async in the half of shared memory that is not being computed on; within a chunk
+// the warps do not wait for one another.
+// A request's state lies at the start of its slot, head by head, each head as [RPT][dv][NP] (see delta_shape); a
+// portion that begins at position 0 starts from zero whatever the slot held.
 #include "common.cuh"
 #include <math.h>
 
@@ -21,7 +24,7 @@ __device__ __forceinline__ float softplus_d(float x) { return x > 20.f ? x : log
 
 // xc: fp32 rows [q: G*dk | k: G*dk | ...] (the convolution's output), normalised in place.
 // ba: rows of the projection holding b (H values at b_off) and a (H values at a_off) in the compute dtype.
-// bg: fp32 [T, 2H]: beta, then g.
+// bg: fp32 [T, 2H + G]: beta, then g, then q . k of the prepared vectors per query/key head.
 template <typename T>
 __global__ void __launch_bounds__(128) delta_prepare_kernel(float* __restrict__ xc, long long xc_stride, const T* __restrict__ ba,
     long long ba_stride, int b_off, int a_off, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
@@ -30,17 +33,26 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* __restrict__ 
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float* row = xc + (size_t)t * xc_stride;
-  for (int vec = warp; vec < 2 * G; vec += nwarps) {
-    float* x = row + (size_t)vec * dk;
-    float ss = 0.f;
-    for (int i = lane; i < dk; i += 32) ss += x[i] * x[i];
-    const float f = rsqrtf(warp_sum(ss) + 1e-6f) * (vec < G ? q_scale : 1.f);
-    for (int i = lane; i < dk; i += 32) x[i] *= f;
+  float* bgr = bg + (size_t)t * (2 * H + G);
+  for (int gh = warp; gh < G; gh += nwarps) {          // a warp takes the query and the key of one head
+    float* q = row + (size_t)gh * dk;
+    float* k = row + (size_t)(G + gh) * dk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = lane; i < dk; i += 32) { sq += q[i] * q[i]; sk += k[i] * k[i]; }
+    const float fq = rsqrtf(warp_sum(sq) + 1e-6f) * q_scale, fk = rsqrtf(warp_sum(sk) + 1e-6f);
+    float dot = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+      const float a = q[i] * fq, b = k[i] * fk;
+      q[i] = a; k[i] = b;
+      dot = fmaf(a, b, dot);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) bgr[2 * H + gh] = dot;
   }
   const T* r = ba + (size_t)t * ba_stride;
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    bg[(size_t)t * 2 * H + h] = 1.f / (1.f + expf(-to_f32<T>(r[b_off + h])));
-    bg[(size_t)t * 2 * H + H + h] = expf(-expf(a_log[h]) * softplus_d(to_f32<T>(r[a_off + h]) + dt_bias[h]));
+    bgr[h] = 1.f / (1.f + expf(-to_f32<T>(r[b_off + h])));
+    bgr[H + h] = expf(-expf(a_log[h]) * softplus_d(to_f32<T>(r[a_off + h]) + dt_bias[h]));
   }
 }
 
@@ -59,13 +71,45 @@ SI_EXPORT int si_delta_prepare(float* xc, long long xc_stride, const void* ba, i
 
 #define DELTA_CHUNK 16
 
-// RPT: rows of a column that a thread keeps; NP = ceil(dk / RPT) rounded up to a power of two, at most 32.
+__device__ __forceinline__ void delta_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void delta_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
+// The shape for a state of dk x dv: rows a thread (RPT, a multiple of 4) and parts a column (NP, a power of two up to 32,
+// RPT * NP >= dk). Few rows a thread and many parts: a sequence's tokens are a chain of dependent steps, and what
+// shortens the chain and gives a multiprocessor more warps to choose from counts for more than the shuffles it adds.
+// Thread (column j, part p) keeps, for c < RPT / 4, the four rows (c * NP + p) * 4 .. + 3 of column j (so that the parts
+// read neighbouring 16-byte words of q and k). A head's state lies in the slot as [RPT][dv][NP]: entry
+// ((r * dv + j) * NP + p) is the thread's r-th row, so that a block reads and writes whole lines whatever cut of the
+// columns it has.
+struct DeltaShape { int rpt, np; };
+static DeltaShape delta_shape(int dk) {
+  DeltaShape s;
+  s.rpt = ((dk + 31) / 32 + 3) / 4 * 4;
+  int parts = 1;
+  while (parts * s.rpt < dk) parts *= 2;
+  s.np = parts;
+  return s;
+}
+// fp32 entries of one head's state in a slot
+SI_EXPORT long long si_delta_state_floats(int dk, int dv) {
+  if (dk <= 0 || dv <= 0 || dk > 1024) return -1;
+  const DeltaShape s = delta_shape(dk);
+  return (long long)s.rpt * s.np * dv;
+}
+
+// RPT: rows of a column that a thread keeps, as RPT / 2 pairs (the sums and the update run two rows at a time on the
+// packed fp32 instructions). Shared memory: two buffers of CHUNK tokens of [q: RPT * NP | k: RPT * NP | v: cols |
+// beta, g, q . k, -] (rows beyond dk stay zero), filled by cp.async one chunk ahead of the sums.
 template <int RPT>
 __global__ void __launch_bounds__(256) delta_scan_kernel(const float* __restrict__ xc, long long xc_stride,
-    const float* __restrict__ bg, float* __restrict__ state, long long state_stride, float* __restrict__ y,
+    const float* __restrict__ bg, int bg_width, float* __restrict__ state, long long state_stride, float* __restrict__ y,
     long long y_stride, const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ slots,
     int G, int H, int dk, int dv, int NP, int cols) {
-  extern __shared__ float sm[];                 // [CHUNK][2 * dk + cols + 2]
+  extern __shared__ __align__(16) float sm[];
   pdl_prologue();
   const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
   const int row0 = q_start[s], n = q_start[s + 1] - row0;
@@ -75,98 +119,125 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(const float* __restrict
   const int p = threadIdx.x % NP, jl = threadIdx.x / NP;
   const int j = j0 + jl;
   const bool col_ok = jl < cols && j < dv;
-  float* S = state + (size_t)slots[s] * state_stride + (size_t)h * dk * dv;
-  float st[RPT];
+  float* S = state + (size_t)slots[s] * state_stride + (size_t)h * RPT * NP * dv + (size_t)(col_ok ? j : 0) * NP + p;
+  const size_t s_step = (size_t)dv * NP;
+  float2 st[RPT / 2];
 #pragma unroll
-  for (int r = 0; r < RPT; ++r) {
-    const int i = r * NP + p;
-    st[r] = (col_ok && i < dk && pos0 > 0) ? S[(size_t)i * dv + j] : 0.f;
+  for (int r = 0; r < RPT / 2; ++r) {
+    st[r].x = (col_ok && pos0 > 0) ? S[(size_t)(2 * r) * s_step] : 0.f;
+    st[r].y = (col_ok && pos0 > 0) ? S[(size_t)(2 * r + 1) * s_step] : 0.f;
   }
-  const int per_tok = 2 * dk + cols + 2;
+  const int dkp = RPT * NP;
+  const int per_tok = 2 * dkp + ((cols + 3) & ~3) + 4;
+  for (int idx = threadIdx.x; idx < 2 * DELTA_CHUNK * per_tok; idx += blockDim.x) sm[idx] = 0.f;
+  __syncthreads();
   const size_t q_off = (size_t)g * dk, k_off = (size_t)(G + g) * dk, v_off = (size_t)2 * G * dk + (size_t)h * dv + j0;
-  for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK) {
+  const bool wide = dk % 4 == 0 && xc_stride % 4 == 0 && ((uintptr_t)xc & 15) == 0;      // q and k rows in 16-byte pieces
+  // what this thread copies of every token, found once: its first piece of [q | k] (further ones lie blockDim pieces
+  // on), and one of the token's small values (a value column, or beta, g, q . k)
+  const int unit = wide ? 4 : 1, pieces = 2 * dk / unit, per_half = dk / unit;
+  const int extra = threadIdx.x < cols + 3 ? threadIdx.x : -1;
+  long long extra_src = 0;
+  int extra_dst = 0;
+  bool extra_bg = false;
+  if (extra >= cols) {
+    const int w = extra - cols;
+    extra_bg = true;
+    extra_src = w == 0 ? h : w == 1 ? H + h : 2 * H + g;
+    extra_dst = per_tok - 4 + w;
+  } else if (extra >= 0) {
+    extra_src = (long long)v_off + extra;
+    extra_dst = 2 * dkp + extra;
+  }
+  const bool extra_ok = extra >= 0 && (extra_bg || j0 + extra < dv);
+  auto fetch = [&](int c0, int buf) {
+    float* dst = sm + (size_t)buf * DELTA_CHUNK * per_tok;
     const int cn = min(DELTA_CHUNK, n - c0);
-    __syncthreads();                            // the chunk before is done with
-    for (int idx = threadIdx.x; idx < cn * per_tok; idx += blockDim.x) {
-      const int tt = idx / per_tok, e = idx - tt * per_tok;
-      const float* row = xc + (size_t)(row0 + c0 + tt) * xc_stride;
-      float v;
-      if (e < dk) v = row[q_off + e];
-      else if (e < 2 * dk) v = row[k_off + e - dk];
-      else if (e < 2 * dk + cols) v = (j0 + e - 2 * dk < dv) ? row[v_off + e - 2 * dk] : 0.f;
-      else v = bg[(size_t)(row0 + c0 + tt) * 2 * H + (e - 2 * dk - cols) * H + h];      // beta, then g
-      sm[idx] = v;
+    const float* row = xc + (size_t)(row0 + c0) * xc_stride;
+    const float* bgr = bg + (size_t)(row0 + c0) * bg_width;
+    for (int tt = 0; tt < cn; ++tt, row += xc_stride, bgr += bg_width, dst += per_tok) {
+      for (int t = threadIdx.x; t < pieces; t += blockDim.x) {
+        const bool is_q = t < per_half;
+        const int i = (is_q ? t : t - per_half) * unit;
+        if (wide) delta_cp16(dst + (is_q ? 0 : dkp) + i, row + (is_q ? q_off : k_off) + i);
+        else delta_cp4(dst + (is_q ? 0 : dkp) + i, row + (is_q ? q_off : k_off) + i);
+      }
+      if (extra_ok) delta_cp4(dst + extra_dst, (extra_bg ? bgr : row) + extra_src);
     }
-    __syncthreads();
-    for (int tt = 0; tt < cn; ++tt) {
-      const float* qs = sm + (size_t)tt * per_tok;
-      const float* ks = qs + dk;
-      float sk = 0.f, sq = 0.f, qk = 0.f;
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  fetch(0, 0);
+  int buf = 0;
+  for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK, buf ^= 1) {
+    const int cn = min(DELTA_CHUNK, n - c0);
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();                            // this chunk has arrived, and everyone is done with the other buffer
+    if (c0 + DELTA_CHUNK < n) fetch(c0 + DELTA_CHUNK, buf ^ 1);
+    const float* tok = sm + (size_t)buf * DELTA_CHUNK * per_tok;
+    float* yp = y + (size_t)(row0 + c0) * y_stride + (size_t)h * dv + j;
+    for (int tt = 0; tt < cn; ++tt, tok += per_tok, yp += y_stride) {
+      const float4* q4 = reinterpret_cast<const float4*>(tok) + p;
+      const float4* k4 = reinterpret_cast<const float4*>(tok + dkp) + p;
+      float2 kk[RPT / 2];
+      float2 sk0 = make_float2(0.f, 0.f), sq0 = sk0;
 #pragma unroll
-      for (int r = 0; r < RPT; ++r) {
-        const int i = r * NP + p;
-        const float kv = i < dk ? ks[i] : 0.f, qv = i < dk ? qs[i] : 0.f;
-        sk = fmaf(kv, st[r], sk);
-        sq = fmaf(qv, st[r], sq);
-        qk = fmaf(qv, kv, qk);
+      for (int c = 0; c < RPT / 4; ++c) {
+        const float4 kv = k4[c * NP], qv = q4[c * NP];
+        kk[2 * c] = make_float2(kv.x, kv.y);
+        kk[2 * c + 1] = make_float2(kv.z, kv.w);
+        sk0 = __ffma2_rn(kk[2 * c], st[2 * c], sk0);
+        sq0 = __ffma2_rn(make_float2(qv.x, qv.y), st[2 * c], sq0);
+        sk0 = __ffma2_rn(kk[2 * c + 1], st[2 * c + 1], sk0);
+        sq0 = __ffma2_rn(make_float2(qv.z, qv.w), st[2 * c + 1], sq0);
       }
-      for (int o = 1; o < NP; o <<= 1) {
-        sk += __shfl_xor_sync(0xffffffffu, sk, o);
-        sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        qk += __shfl_xor_sync(0xffffffffu, qk, o);
-      }
-      const float beta = qs[2 * dk + cols], gt = qs[2 * dk + cols + 1];
-      const float vj = qs[2 * dk + (jl < cols ? jl : 0)];
-      const float u = beta * (vj - gt * sk);
+      float sk = sk0.x + sk0.y, sq = sq0.x + sq0.y;
 #pragma unroll
-      for (int r = 0; r < RPT; ++r) {
-        const int i = r * NP + p;
-        const float kv = i < dk ? ks[i] : 0.f;
-        st[r] = fmaf(kv, u, gt * st[r]);
+      for (int o = 1; o < 32; o <<= 1) {
+        if (o < NP) {                           // the same for every thread
+          sk += __shfl_xor_sync(0xffffffffu, sk, o);
+          sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        }
       }
-      if (p == 0 && col_ok) y[(size_t)(row0 + c0 + tt) * y_stride + (size_t)h * dv + j] = fmaf(qk, u, gt * sq);
+      const float4 sc = *reinterpret_cast<const float4*>(tok + per_tok - 4);      // beta, g, q . k
+      const float vj = col_ok ? tok[2 * dkp + jl] : 0.f;
+      const float u = sc.x * (vj - sc.y * sk);
+      const float2 u2 = make_float2(u, u), g2 = make_float2(sc.y, sc.y);
+#pragma unroll
+      for (int r = 0; r < RPT / 2; ++r) st[r] = __ffma2_rn(kk[r], u2, __fmul2_rn(g2, st[r]));
+      if (p == 0 && col_ok) *yp = fmaf(sc.z, u, sc.y * sq);
     }
   }
   if (col_ok) {
 #pragma unroll
-    for (int r = 0; r < RPT; ++r) {
-      const int i = r * NP + p;
-      if (i < dk) S[(size_t)i * dv + j] = st[r];
+    for (int r = 0; r < RPT / 2; ++r) {
+      S[(size_t)(2 * r) * s_step] = st[r].x;
+      S[(size_t)(2 * r + 1) * s_step] = st[r].y;
     }
   }
 }
 
-// The launch shape for a state of dk x dv: rows a thread (RPT), parts a column (NP, a power of two up to 32),
-// columns a block.
-static void delta_shape(int dk, int dv, int* rpt, int* np, int* cols) {
-  int r = 4;
-  while (r < 64 && (dk + r - 1) / r > 32) r *= 2;       // at most 32 parts
-  if (dk >= 64 && r < 8) r = 8;
-  if (dk >= 128 && r < 16) r = 16;
-  int parts = 1;
-  while (parts * r < dk) parts *= 2;
-  *rpt = r;
-  *np = parts;
-  int c = 256 / parts;
-  if (c > dv) c = dv;
-  if (c < 1) c = 1;
-  *cols = c;
-}
-
-SI_EXPORT int si_delta_scan(const float* xc, long long xc_stride, const float* bg, float* state, long long state_stride,
-                            float* y, long long y_stride, const int* q_start, const int* ctx_len, const int* slots,
-                            int num_seqs, int G, int H, int dk, int dv, cudaStream_t stream) {
+SI_EXPORT int si_delta_scan(const float* xc, long long xc_stride, const float* bg, int bg_width, float* state,
+                            long long state_stride, float* y, long long y_stride, const int* q_start, const int* ctx_len,
+                            const int* slots, int num_seqs, int G, int H, int dk, int dv, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
-  if (G <= 0 || H % G || dk <= 0 || dv <= 0 || dk > 2048 || H > 65535) return -2;
-  int rpt, np, cols;
-  delta_shape(dk, dv, &rpt, &np, &cols);
-  if (rpt * np < dk) return -2;
+  if (G <= 0 || H % G || dk <= 0 || dv <= 0 || dk > 1024 || H > 65535 || bg_width < 2 * H + G) return -2;
+  const DeltaShape sh = delta_shape(dk);
+  if (sh.rpt * sh.np < dk) return -2;
+  if (state_stride < (long long)H * sh.rpt * sh.np * dv) return -2;
+  // columns a block: as many as 256 threads hold, fewer while the blocks do not fill the device (a block's tokens are a
+  // chain of dependent steps, so more blocks of fewer columns finish sooner); never less than a warp
+  int cols = 256 / sh.np;
+  if (cols > dv) cols = dv;
+  if (cols < 1) cols = 1;
+  const long long per = (long long)num_seqs * H;
+  while (cols > 1 && (cols / 2) * sh.np >= 32 && per * ((dv + cols - 1) / cols) < si_sm_count()) cols /= 2;
   const int zb = (dv + cols - 1) / cols;
   if (zb > 65535) return -2;
-  const int threads = ((cols * np + 31) / 32) * 32;
-  const size_t smem = (size_t)DELTA_CHUNK * (2 * dk + cols + 2) * sizeof(float);
+  const int threads = ((cols * sh.np + 31) / 32) * 32;
+  const size_t smem = (size_t)2 * DELTA_CHUNK * (2 * sh.np * sh.rpt + ((cols + 3) & ~3) + 4) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   const dim3 grid(num_seqs, H, zb), block(threads);
+  const int np = sh.np;
 #define DELTA_LAUNCH(R)                                                                                              \
   {                                                                                                                  \
     static size_t configured = 0;                                                                                    \
@@ -175,14 +246,20 @@ SI_EXPORT int si_delta_scan(const float* xc, long long xc_stride, const float* b
         return -2;                                                                                                   \
       configured = smem;                                                                                             \
     }                                                                                                                \
-    si_launch(delta_scan_kernel<R>, grid, block, smem, stream, xc, xc_stride, bg, state, state_stride, y, y_stride,  \
-              q_start, ctx_len, slots, G, H, dk, dv, np, cols);                                                      \
+    si_launch(delta_scan_kernel<R>, grid, block, smem, stream, xc, xc_stride, bg, bg_width, state, state_stride, y,  \
+              y_stride, q_start, ctx_len, slots, G, H, dk, dv, np, cols);                                            \
   }
-  if (rpt == 4) DELTA_LAUNCH(4)
-  else if (rpt == 8) DELTA_LAUNCH(8)
-  else if (rpt == 16) DELTA_LAUNCH(16)
-  else if (rpt == 32) DELTA_LAUNCH(32)
-  else DELTA_LAUNCH(64)
+  switch (sh.rpt) {                          // dk up to 2048: up to 64 rows a thread
+    case 4: DELTA_LAUNCH(4) break;
+    case 8: DELTA_LAUNCH(8) break;
+    case 12: DELTA_LAUNCH(12) break;
+    case 16: DELTA_LAUNCH(16) break;
+    case 20: DELTA_LAUNCH(20) break;
+    case 24: DELTA_LAUNCH(24) break;
+    case 28: DELTA_LAUNCH(28) break;
+    case 32: DELTA_LAUNCH(32) break;
+    default: return -2;
+  }
 #undef DELTA_LAUNCH
   return si_last_error();
 }

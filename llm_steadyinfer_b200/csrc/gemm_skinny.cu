@@ -39,6 +39,11 @@ struct SkinnyRope {
   int* status;
   int act;                   // plain store only: 1 = the square of relu of the sum (rounded to bf16 first, as a stored
                              // product followed by the activation kernel gives); 0 = the sum as it is
+  // the gated epilogue only: glu = 1 takes the form with limits, g = min(gate + b, limit), u = clamp(up + b, -limit, limit),
+  // out = g * sigmoid(alpha * g) * (u + 1), with the biases of the stacked columns (fp32, may be null)
+  int glu;
+  const float* glu_bias;
+  float glu_limit, glu_alpha;
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -210,8 +215,18 @@ gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __rest
       for (int w = 0; w < WARPS; ++w) { gs += red[w][mt][ln][e]; us += red[w][mt][ln][e + 2]; }
       const int f = blockIdx.x * 8 + (ln >> 2);
       const int m = mt * 8 + (ln & 3) * 2 + e;
-      if (2 * f < N && m < M)
-        store_out<TO>(out + (size_t)m * ldo + f, silu_mul(__bfloat162float(__float2bfloat16_rn(gs)), __bfloat162float(__float2bfloat16_rn(us))));
+      if (2 * f < N && m < M) {
+        float gv = __bfloat162float(__float2bfloat16_rn(gs)), uv = __bfloat162float(__float2bfloat16_rn(us));
+        if (rope.glu) {
+          const int gc = blockIdx.x * 16 + (ln >> 2);             // the gate's place among the stacked columns; its up: 8 on
+          if (rope.glu_bias) { gv += rope.glu_bias[gc]; uv += rope.glu_bias[gc + 8]; }
+          gv = fminf(gv, rope.glu_limit);
+          uv = fminf(fmaxf(uv, -rope.glu_limit), rope.glu_limit);
+          store_out<TO>(out + (size_t)m * ldo + f, gv / (1.f + expf(-rope.glu_alpha * gv)) * (uv + 1.f));
+        } else {
+          store_out<TO>(out + (size_t)m * ldo + f, silu_mul(gv, uv));
+        }
+      }
     }
   } else {
     // threads (mt, lane, e) add the warps' partial sums in warp order and store
@@ -293,6 +308,18 @@ SI_EXPORT int si_gemm_skinny_swiglu(const void* x, long long ldx, const void* W,
   if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
   const unsigned blocks = (unsigned)(F / 8);
   skinny_dispatch<bf16, true, false>(blocks, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, 2 * F, K, SkinnyRope());
+  return si_last_error();
+}
+
+// The same with the gated activation's limited form (see SkinnyRope::glu); `bias`: fp32 [2F] in the rows' order, or null.
+SI_EXPORT int si_gemm_skinny_glu_limited(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
+                                         int M, int F, int K, const float* bias, float limit, float alpha, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  if (M > 16 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (F % 8)) return -2;
+  if (((uintptr_t)x % 16) || ((uintptr_t)W % 16)) return -2;
+  SkinnyRope r = SkinnyRope();
+  r.glu = 1; r.glu_bias = bias; r.glu_limit = limit; r.glu_alpha = alpha;
+  skinny_dispatch<bf16, true, false>((unsigned)(F / 8), stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, 2 * F, K, r);
   return si_last_error();
 }
 

@@ -67,7 +67,11 @@ __device__ __forceinline__ void add_row32(float* dst, const float (&v)[32], int 
 }
 
 // What the epilogue does with a tile: store it, store silu(gate) * up of it, or add it into an fp32 tensor.
-enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2, EPI_RELU2 = 3 };
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2, EPI_RELU2 = 3, EPI_GLU_LIMITED = 4 };
+
+// What EPI_GLU_LIMITED needs: the biases of the stacked gate/up columns (fp32, in the columns' order; may be null), the
+// limit and the sigmoid's factor.
+struct EpiArgs { const float* bias; float limit, alpha; };
 
 // The square of relu of every sum, each rounded to bf16 first (what a stored product followed by the activation
 // kernel gives).
@@ -103,10 +107,50 @@ __device__ __forceinline__ void store_swiglu16(bf16* dst, const float (&v)[32], 
   }
 }
 
+// The gated activation with limits, as store_swiglu16 lays the columns out: g = min(gate + b, limit),
+// u = clamp(up + b, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1); gate and up rounded to bf16 first.
+__device__ __forceinline__ void store_glu_limited16(bf16* dst, const float (&v)[32], const float* bias, float limit, float alpha,
+                                                    int valid, bool vec) {
+  float o[16], b[32];
+  if (bias && valid == 16) {                     // the 32 biases of these columns in eight 16-byte loads
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 t = reinterpret_cast<const float4*>(bias)[i];
+      b[4 * i] = t.x; b[4 * i + 1] = t.y; b[4 * i + 2] = t.z; b[4 * i + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) b[i] = (bias && 8 * (i / 16) + i % 8 < valid) ? bias[i] : 0.f;
+  }
+#pragma unroll
+  for (int g = 0; g < 2; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float gv = __bfloat162float(__float2bfloat16_rn(v[16 * g + i])), uv = __bfloat162float(__float2bfloat16_rn(v[16 * g + 8 + i]));
+      gv += b[16 * g + i]; uv += b[16 * g + 8 + i];
+      gv = fminf(gv, limit);
+      uv = fminf(fmaxf(uv, -limit), limit);
+      o[8 * g + i] = gv / (1.f + __expf(-alpha * gv)) * (uv + 1.f);
+    }
+  if (vec && valid == 16) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 raw;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[8 * i + 2 * j], o[8 * i + 2 * j + 1]);
+      reinterpret_cast<uint4*>(dst)[i] = raw;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) if (i < valid) dst[i] = __float2bfloat16_rn(o[i]);
+  }
+}
+
 template <int STAGES, typename TO, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
-                 TO* __restrict__ out, long long ldo, int M, int N, int K, int* status) {
+                 TO* __restrict__ out, long long ldo, int M, int N, int K, int* status, const EpiArgs epi) {
   constexpr int BM = 128, BN = 256, BK = 64;
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   extern __shared__ unsigned char smem_dyn[];
@@ -217,6 +261,9 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
           const int n = n0 + h * 128 + c * 32;
           if (row < M && n < N) {
             if (EPI == EPI_SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
+            else if (EPI == EPI_GLU_LIMITED)
+              store_glu_limited16((bf16*)out + (size_t)row * ldo + n / 2, v[c], epi.bias ? epi.bias + n : nullptr, epi.limit, epi.alpha,
+                                  min(16, (N - n) / 2), vec);
             else if (EPI == EPI_ADD) add_row32((float*)out + (size_t)row * ldo + n, v[c], min(32, N - n), vec4);
             else {
               if (EPI == EPI_RELU2) relu2_row32(v[c]);
@@ -246,7 +293,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
 template <int STAGES, typename TO, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192)
 gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
-                      TO* __restrict__ out, long long ldo, int M, int N, int K, int* status) {
+                      TO* __restrict__ out, long long ldo, int M, int N, int K, int* status, const EpiArgs epi) {
   constexpr int BM = 128, BN = 256, BK = 64;             // BM, and BN / 2 rows of W, per CTA
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2;
   extern __shared__ unsigned char smem_dyn[];
@@ -374,6 +421,9 @@ gemm_tc05_pair_kernel(const __grid_constant__ CUtensorMap amap, const __grid_con
           const int n = n0 + h * 128 + c * 32;
           if (row < M && n < N) {
             if (EPI == EPI_SWIGLU) store_swiglu16((bf16*)out + (size_t)row * ldo + n / 2, v[c], min(16, (N - n) / 2), vec);
+            else if (EPI == EPI_GLU_LIMITED)
+              store_glu_limited16((bf16*)out + (size_t)row * ldo + n / 2, v[c], epi.bias ? epi.bias + n : nullptr, epi.limit, epi.alpha,
+                                  min(16, (N - n) / 2), vec);
             else if (EPI == EPI_ADD) add_row32((float*)out + (size_t)row * ldo + n, v[c], min(32, N - n), vec4);
             else {
               if (EPI == EPI_RELU2) relu2_row32(v[c]);
@@ -401,7 +451,7 @@ static bool pair_enabled() {
 
 template <typename TO, int EPI>
 static int launch_pair(const CUtensorMap& am, const CUtensorMap& bm_half, void* out, long long ldo, int M, int N, int K,
-                       int* status, cudaStream_t stream) {
+                       int* status, cudaStream_t stream, EpiArgs epi = EpiArgs()) {
   constexpr int STAGES = 6;
   const size_t smem = (size_t)STAGES * (128 * 64 * 2 + 128 * 64 * 2) + 1024;
   auto k = gemm_tc05_pair_kernel<STAGES, TO, EPI>;
@@ -410,20 +460,20 @@ static int launch_pair(const CUtensorMap& am, const CUtensorMap& bm_half, void* 
   const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
   const int pairs = tiles < si_sm_count() / 2 ? tiles : si_sm_count() / 2;
   if (pairs < 1) return -2;
-  si_launch(k, dim3(2 * pairs), dim3(192), smem, stream, am, bm_half, (TO*)out, ldo, M, N, K, status);
+  si_launch(k, dim3(2 * pairs), dim3(192), smem, stream, am, bm_half, (TO*)out, ldo, M, N, K, status, epi);
   return si_last_error();
 }
 
 template <int STAGES, typename TO, int EPI>
 static int launch(const CUtensorMap& am, const CUtensorMap& bm, void* out, long long ldo, int M, int N, int K,
-                  int* status, cudaStream_t stream) {
+                  int* status, cudaStream_t stream, EpiArgs epi = EpiArgs()) {
   const size_t smem = (size_t)STAGES * (128 * 64 * 2 + 256 * 64 * 2) + 1024;
   auto k = gemm_tc05_kernel<STAGES, TO, EPI>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + 127) / 128) * ((N + 255) / 256);
   const int blocks = tiles < si_sm_count() ? tiles : si_sm_count();
-  si_launch(k, dim3(blocks), dim3(192), smem, stream, am, bm, (TO*)out, ldo, M, N, K, status);
+  si_launch(k, dim3(blocks), dim3(192), smem, stream, am, bm, (TO*)out, ldo, M, N, K, status, epi);
   return si_last_error();
 }
 
@@ -476,6 +526,23 @@ SI_EXPORT int si_gemm_tc05_swiglu(const void* x, long long ldx, const void* wmap
   if (use_pair(M, wmap_half)) return launch_pair<bf16, EPI_SWIGLU>(am, *(const CUtensorMap*)wmap_half, out, ldo, M, 2 * F, K, status, stream);
   const CUtensorMap& bm = *(const CUtensorMap*)wmap;
   return launch<4, bf16, EPI_SWIGLU>(am, bm, out, ldo, M, 2 * F, K, status, stream);
+}
+
+// out[M, F] (bf16) = the gated activation with limits (see store_glu_limited16) of the stacked projection x[M, K] W[2F, K]^T
+// whose rows are interleaved in groups of 8; `bias`: fp32 [2F] in the rows' order, or null.
+SI_EXPORT int si_gemm_tc05_glu_limited(const void* x, long long ldx, const void* wmap, const void* wmap_half, void* out,
+                                       long long ldo, int M, int F, int K, const float* bias, float limit, float alpha,
+                                       int* status, cudaStream_t stream) {
+  if (M <= 0 || F <= 0) return 0;
+  if (F % 8) return -2;
+  CUtensorMap am;
+  const int rc = gemm_tc05_common(x, ldx, wmap, &am, M, K);
+  if (rc) return rc;
+  EpiArgs epi;
+  epi.bias = bias; epi.limit = limit; epi.alpha = alpha;
+  if (use_pair(M, wmap_half))
+    return launch_pair<bf16, EPI_GLU_LIMITED>(am, *(const CUtensorMap*)wmap_half, out, ldo, M, 2 * F, K, status, stream, epi);
+  return launch<4, bf16, EPI_GLU_LIMITED>(am, *(const CUtensorMap*)wmap, out, ldo, M, 2 * F, K, status, stream, epi);
 }
 
 // out[M, N] (bf16) = relu(x W^T)^2: a feed-forward's activation in the epilogue of its first product.

@@ -663,6 +663,23 @@ def gemm_skinny_swiglu(a, w, out, checked: bool = False) -> None:
            f"gemm_skinny_swiglu(M={M}, F={F}, K={K})")
 
 
+def gemm_skinny_glu_limited(a, w, bias, out, limit: float, alpha: float, checked: bool = False) -> None:
+    """out[M,F] = g * sigmoid(alpha g) * (u + 1), g = min(gate + bias, limit), u = clamp(up + bias, -limit, limit), of
+    a[M,K] @ w[2F,K]^T for M <= 16, the rows of w (and the entries of ``bias``, fp32 [2F] or None) interleaved in groups of
+    8: the activation runs in the product's epilogue."""
+    _cuda(a, w, bias, out)
+    M, K = a.shape
+    F = out.shape[1]
+    _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16,
+          "gemm_skinny_glu_limited: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
+    _need(checked or gemm_skinny_ok(a, w, out), "gemm_skinny_glu_limited: bf16 inputs, at most 16 rows, K a multiple of 8, 16-byte aligned rows")
+    _f32v(bias, "bias", 2 * F)
+    f = _fn("gemm_skinny", "si_gemm_skinny_glu_limited",
+            [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_f, _c_f, _c_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, F, K, _ptr(bias), float(limit), float(alpha),
+             _stream()), f"gemm_skinny_glu_limited(M={M}, F={F}, K={K})")
+
+
 def gemm_skinny_qkv_rope(a, w, out, positions, row_seq, inv_freq, block_table, k_cache, v_cache, page_size: int,
                          num_seqs: int, H: int, KV: int, hs: int, status=None) -> None:
     """The stacked q/k/v projection of at most 16 rows with what ``rope_kv_write`` would do next in its epilogue:
@@ -762,6 +779,22 @@ def gemm_tc05_add(a, w, resid, status=None) -> None:
     half = _weight_map(w, 128) if M > 128 else None
     _check(f(_ptr(a), a.stride(0), _weight_map(w), half, _ptr(resid), resid.stride(0), M, N, K, _ptr(status), _stream()),
            f"gemm_tc05_add(M={M}, N={N}, K={K})")
+
+
+def gemm_tc05_glu_limited(a, w, bias, out, limit: float, alpha: float, status=None) -> None:
+    """``gemm_skinny_glu_limited`` for many rows, on the tcgen05 tensor cores."""
+    _cuda(a, w, bias, out, status)
+    M, K = a.shape
+    F = out.shape[1]
+    _need(w.shape == (2 * F, K) and out.shape[0] == M and F % 8 == 0 and out.dtype == torch.bfloat16 and out.stride(1) == 1,
+          "gemm_tc05_glu_limited: w must be [2F, K], out [M, F] bf16, F a multiple of 8")
+    _need(gemm_tc05_ok(a, w, out), "gemm_tc05_glu_limited: bf16 inputs, K a multiple of 8, 16-byte aligned rows")
+    _f32v(bias, "bias", 2 * F)
+    f = _fn("gemm_tc05", "si_gemm_tc05_glu_limited",
+            [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p, _c_f, _c_f, _c_p, _c_p])
+    half = _weight_map(w, 128) if M > 128 else None
+    _check(f(_ptr(a), a.stride(0), _weight_map(w), half, _ptr(out), out.stride(0), M, F, K, _ptr(bias), float(limit), float(alpha),
+             _ptr(status), _stream()), f"gemm_tc05_glu_limited(M={M}, F={F}, K={K})")
 
 
 def gemm_tc05_relu2(a, w, out, status=None) -> None:
@@ -1250,15 +1283,36 @@ def diff_combine(a, gate, out, H: int, dv: int, ratio: int, lam: float, eps: flo
 
 # ---- gated delta rule ------------------------------------------------------------------------------------------------
 
+def delta_state_floats(dk: int, dv: int) -> int:
+    """fp32 entries of one head's dk x dv state as the scan kernel keeps it in a slot ([rows a thread][dv][parts a column],
+    the rows padded to rows a thread x parts). The same rule as ``delta_shape`` in delta_rule.cu, restated here so that a
+    model's state size is known without the library; ``delta_state_floats_of_library`` asks the library, and a test holds
+    the two together."""
+    if dk <= 0 or dv <= 0 or dk > 1024:
+        raise KernelError(f"delta_scan: a state of {dk} x {dv} is outside what the kernel supports")
+    r = (-(-dk // 32) + 3) // 4 * 4
+    parts = 1
+    while parts * r < dk:
+        parts *= 2
+    return r * parts * dv
+
+
+def delta_state_floats_of_library(dk: int, dv: int) -> int:
+    lib = build.load("delta_rule")
+    lib.si_delta_state_floats.restype = _c_ll
+    return lib.si_delta_state_floats(_c_int(dk), _c_int(dv))
+
+
 def delta_prepare(xc, ba, b_off: int, a_off: int, a_log, dt_bias, bg, G: int, H: int, dk: int, q_scale: float) -> None:
     """``xc`` fp32 rows [q: G*dk | k: G*dk | ...]: q and k become unit vectors per head (x / sqrt(sum(x^2) + 1e-6)), q times
     ``q_scale``. ``ba``: rows holding H raw values b at column ``b_off`` and H raw values a at ``a_off``;
-    ``bg`` fp32 [T, 2H] receives beta = sigmoid(b) and g = exp(-exp(a_log) * softplus(a + dt_bias))."""
+    ``bg`` fp32 [T, 2H + G] receives beta = sigmoid(b), g = exp(-exp(a_log) * softplus(a + dt_bias)) and, per query/key
+    head, q . k of the prepared vectors."""
     _cuda(xc, ba, a_log, dt_bias, bg)
     T = xc.shape[0]
     _need(xc.dtype == torch.float32 and xc.stride(1) == 1 and xc.shape[1] >= 2 * G * dk, "delta_prepare: xc must be fp32 rows")
     _need(ba.shape[0] == T and ba.stride(1) == 1 and ba.shape[1] >= max(b_off, a_off) + H, "delta_prepare: ba rows")
-    _need(bg.dtype == torch.float32 and bg.is_contiguous() and bg.shape == (T, 2 * H), "delta_prepare: bg must be fp32 [T, 2H]")
+    _need(bg.dtype == torch.float32 and bg.is_contiguous() and bg.shape == (T, 2 * H + G), "delta_prepare: bg must be fp32 [T, 2H + G]")
     _f32v(a_log, "a_log", H); _f32v(dt_bias, "dt_bias", H)
     f = _fn("delta_rule", "si_delta_prepare",
             [_c_p, _c_ll, _c_p, _c_int, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_p])
@@ -1268,21 +1322,23 @@ def delta_prepare(xc, ba, b_off: int, a_off: int, a_log, dt_bias, bg, G: int, H:
 
 def delta_scan(xc, bg, state, y, q_start, ctx_len, slots, num_seqs: int, G: int, H: int, dk: int, dv: int) -> None:
     """The gated delta rule over every sequence's rows of this step: per head S <- g S; u = beta (v - S^T k);
-    S <- S + k u^T; o = S^T q, from and into the first H*dk*dv floats of ``state[slot]`` (fp32 [H, dk, dv]; from zero
-    for a portion that starts at position 0). ``xc`` fp32 [T, 2*G*dk + H*dv] = [q | k | v] as ``delta_prepare`` leaves
-    it, ``bg`` fp32 [T, 2H], ``y`` fp32 [T, H*dv]. Head h reads q/k head h // (H / G)."""
+    S <- S + k u^T; o = S^T q, from and into the first ``H * delta_state_floats(dk, dv)`` floats of ``state[slot]`` (fp32,
+    in the kernel's own order; from zero for a portion that starts at position 0). ``xc`` fp32 [T, 2*G*dk + H*dv] =
+    [q | k | v] and ``bg`` fp32 [T, 2H + G] as ``delta_prepare`` leaves them, ``y`` fp32 [T, H*dv]. Head h reads q/k
+    head h // (H / G)."""
     _cuda(xc, bg, state, y, q_start, ctx_len, slots)
     for t, nm in ((q_start, "q_start"), (ctx_len, "ctx_len"), (slots, "slots")):
         _i32(t, nm)
     T = xc.shape[0]
     _need(xc.dtype == torch.float32 and xc.stride(1) == 1 and xc.shape[1] >= 2 * G * dk + H * dv, "delta_scan: xc must be fp32 [T, 2*G*dk + H*dv]")
-    _need(bg.dtype == torch.float32 and bg.is_contiguous() and bg.shape == (T, 2 * H), "delta_scan: bg must be fp32 [T, 2H]")
+    _need(bg.dtype == torch.float32 and bg.is_contiguous() and bg.shape == (T, 2 * H + G), "delta_scan: bg must be fp32 [T, 2H + G]")
     _need(y.dtype == torch.float32 and y.shape == (T, H * dv) and y.stride(1) == 1, "delta_scan: y must be fp32 [T, H*dv]")
-    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= H * dk * dv,
-          "delta_scan: state must be fp32 [slots, >= H*dk*dv]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state.shape[1] >= H * delta_state_floats(dk, dv),
+          "delta_scan: state must be fp32 [slots, >= H * delta_state_floats(dk, dv)]")
     f = _fn("delta_rule", "si_delta_scan",
-            [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
-    _check(f(_ptr(xc), xc.stride(0), _ptr(bg), _ptr(state), state.stride(0), _ptr(y), y.stride(0), _ptr(q_start),
+            [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_ptr(xc), xc.stride(0), _ptr(bg), bg.shape[1], _ptr(state), state.stride(0), _ptr(y), y.stride(0), _ptr(q_start),
              _ptr(ctx_len), _ptr(slots), int(num_seqs), G, H, dk, dv, _stream()), f"delta_scan(heads={H}, dk={dk}, dv={dv})")
 
 

@@ -17,8 +17,8 @@
 
 template <typename T>
 __device__ __forceinline__ void norm_rotate_vector(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ w,
-                                                   float eps, const float* __restrict__ inv_freq, int rd, int interleaved,
-                                                   float fpos, int dk, int lane) {
+                                                   float eps, const float* __restrict__ sc_table, int rd, int interleaved,
+                                                   int dk, int lane) {
   float inv = 1.f;
   if (w) {
     float ss = 0.f;
@@ -43,8 +43,7 @@ __device__ __forceinline__ void norm_rotate_vector(const T* __restrict__ src, T*
       if (interleaved) { f = i >> 1; first = (i & 1) == 0; partner = i ^ 1; }
       else { first = i < half; f = first ? i : i - half; partner = first ? i + half : i - half; }
       const float z = to_f32<T>(src[partner]) * inv * (w ? w[partner] : 1.f);
-      float s, c2;
-      sincosf(fpos * inv_freq[f], &s, &c2);
+      const float s = sc_table[f], c2 = sc_table[half + f];
       y = first ? y * c2 - z * s : y * c2 + z * s;
     }
     keep[c] = y;
@@ -64,6 +63,7 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(T* __restrict__ rows, l
     const int* __restrict__ positions, const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_width,
     T* __restrict__ k_cache, T* __restrict__ v_cache, int num_pages, int page_size, int num_seqs, int NQ, int NK, int NV,
     int dk, int dv, T* __restrict__ q_out, long long q_out_stride, int maps, int* status) {
+  extern __shared__ float sc_table[];                  // the row's sines, then its cosines: rd / 2 each, once for all vectors
   pdl_prologue();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -86,17 +86,19 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(T* __restrict__ rows, l
   const int off = pos % page_size;
   T* row = rows + (size_t)t * row_stride;
   const float fpos = (float)pos;
+  for (int f = threadIdx.x; f < rd / 2; f += blockDim.x) sincosf(fpos * inv_freq[f], &sc_table[f], &sc_table[rd / 2 + f]);
+  __syncthreads();
   const int ratio = NQ / NK;                         // query vectors a key vector
   for (int vec = warp; vec < NQ + NK; vec += nwarps) {
     T* src = row + (size_t)vec * dk;
     if (vec < NQ) {
       const int head = vec / maps, m = vec - head * maps;
       const int place = ((head / ratio) * maps + m) * ratio + head % ratio;       // maps == 1: vec itself
-      norm_rotate_vector<T>(src, q_out + (size_t)t * q_out_stride + (size_t)place * dk, q_w, eps, inv_freq, rd, interleaved,
-                            fpos, dk, lane);
+      norm_rotate_vector<T>(src, q_out + (size_t)t * q_out_stride + (size_t)place * dk, q_w, eps, sc_table, rd, interleaved,
+                            dk, lane);
     } else if (page >= 0) {
       T* dst = k_cache + (((size_t)page * NK + (vec - NQ)) * page_size + off) * dk;
-      norm_rotate_vector<T>(src, dst, k_w, eps, inv_freq, rd, interleaved, fpos, dk, lane);
+      norm_rotate_vector<T>(src, dst, k_w, eps, sc_table, rd, interleaved, dk, lane);
     }
   }
   if (page >= 0 && v_cache) {
@@ -116,13 +118,14 @@ SI_EXPORT int si_qk_prepare(void* rows, int dtype, long long row_stride, const f
   if (num_tokens <= 0) return 0;
   if (dk <= 0 || dk > 640 || rd < 0 || rd > dk || rd % 2 || (rd > 0 && !inv_freq)) return -2;
   if (maps < 1 || NK <= 0 || NQ % NK || NK % maps || (maps > 1 && q_out == rows)) return -2;
+  const size_t smem = (size_t)(rd > 0 ? rd : 1) * sizeof(float);
   if (dtype == SI_BF16)
-    si_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, stream, (__nv_bfloat16*)rows, row_stride, q_w,
+    si_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), smem, stream, (__nv_bfloat16*)rows, row_stride, q_w,
               k_w, eps, inv_freq, rd, interleaved, positions, row_seq, block_table, table_width, (__nv_bfloat16*)k_cache,
               (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, NQ, NK, NV, dk, dv, (__nv_bfloat16*)q_out, q_out_stride,
               maps, status);
   else
-    si_launch(qk_prepare_kernel<float>, dim3(num_tokens), dim3(128), 0, stream, (float*)rows, row_stride, q_w, k_w, eps,
+    si_launch(qk_prepare_kernel<float>, dim3(num_tokens), dim3(128), smem, stream, (float*)rows, row_stride, q_w, k_w, eps,
               inv_freq, rd, interleaved, positions, row_seq, block_table, table_width, (float*)k_cache, (float*)v_cache,
               num_pages, page_size, num_seqs, NQ, NK, NV, dk, dv, (float*)q_out, q_out_stride, maps, status);
   return si_last_error();

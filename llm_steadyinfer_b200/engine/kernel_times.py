@@ -31,6 +31,9 @@ KINDS = {
     "embedding_pair": "embedding", "rmsnorm_rows": "rmsnorm_rows", "attention_general": "attention_general",
     "attn_flex": "attn_flex", "kv_store": "kv_store", "latent_prepare": "latent_prepare", "activation": "activation",
     "gemm_heads": "gemm_heads", "gemm_skinny_relu2": "gemm_skinny_relu2", "gemm_tc05_relu2": "gemm_tc05_relu2", "latent_gather": "latent_gather", "latent_expand_keys": "latent_expand_keys", "causal_conv": "causal_conv", "ssm_scan": "ssm_scan", "gated_part_norm": "gated_part_norm",
+    "add_norm": "add_norm", "qk_prepare": "qk_prepare", "diff_combine": "diff_combine", "delta_prepare": "delta_prepare",
+    "delta_scan": "delta_scan", "head_norm_gate": "head_norm_gate", "softcap": "softcap", "add_bias": "add_bias",
+    "glu_limited": "glu_limited", "gemm_skinny_glu_limited": "gemm_skinny_glu_limited", "gemm_tc05_glu_limited": "gemm_tc05_glu_limited",
 }
 
 

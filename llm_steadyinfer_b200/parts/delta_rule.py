@@ -9,7 +9,8 @@ Per row x, with H heads of value size dv and G query/key heads of size dk (head 
     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q                          S is dk x dv, fp32, zero at the start
     o <- norm_w * o * rsqrt(mean(o^2) + eps) * silu(W_g x)_h                               per head, norm_w of size dv shared
     out = W_o concat_h o
-A request's state is one fp32 vector per slot: ``[S: H * dk * dv | the convolution's last taps - 1 inputs]``; kernels start
+A request's state is one fp32 vector per slot: ``[S, head by head in the scan kernel's layout | the
+convolution's last taps - 1 inputs]``; kernels start
 a portion from it and leave the next portion's behind, so prompts can be cut anywhere and decoding is the same path with
 one row. Norms of q and k, beta, the decay, the state, the sums, the read-out's norm and its gate are fp32 in both
 precisions; the convolution's result stays fp32 on its way into the recurrence.
@@ -42,15 +43,15 @@ class GatedDeltaRule(Mixer):
             raise ValueError(f"gated_delta: {self.H} heads are not a multiple of {self.G} query/key heads")
         if not 1 <= self.taps <= 17:
             raise ValueError(f"gated_delta: {self.taps} convolution taps are not supported (1 to 17)")
-        if self.dk > 2048:
-            raise ValueError("gated_delta: key sizes above 2048 are not supported")
+        if self.dk > 1024:
+            raise ValueError("gated_delta: key sizes above 1024 are not supported")
         self.nqk, self.nv = self.G * self.dk, self.H * self.dv
         self.channels = 2 * self.nqk + self.nv                     # what the convolution runs over: [q | k | v]
         self.g_off = self.channels
         self.b_off = self.g_off + self.nv
         self.a_off = self.b_off + self.H
         self.proj_rows = -(-(self.a_off + self.H) // 8) * 8
-        self.conv_off = self.H * self.dk * self.dv
+        self.conv_off = self.H * ops.delta_state_floats(self.dk, self.dv)        # the scan's part of the slot
         self.w_in = self.w_o = self.conv_w = self.conv_b = self.a_log = self.dt_bias = self.norm_w = None
 
     def weight_shapes(self):
@@ -95,7 +96,7 @@ class GatedDeltaRule(Mixer):
         xc = ctx.buf("delta_conv", (T, C), torch.float32)
         ops.causal_conv(u[:, :C], self.conv_w, self.conv_b, state, self.conv_off, xc, ctx.positions, ctx.row_seq,
                         ctx.q_start, ctx.ctx_len, ctx.slots, ctx.seq_slots, status=ctx.status)
-        bg = ctx.buf("delta_bg", (T, 2 * H), torch.float32)
+        bg = ctx.buf("delta_bg", (T, 2 * H + G), torch.float32)
         ops.delta_prepare(xc, u, self.b_off, self.a_off, self.a_log, self.dt_bias, bg, G, H, dk, dk ** -0.5)
         y = ctx.buf("delta_y", (T, self.nv), torch.float32)
         ops.delta_scan(xc, bg, state, y, ctx.q_start, ctx.ctx_len, ctx.slots, ctx.seq_slots, G, H, dk, dv)

@@ -139,7 +139,9 @@ class LimitedGatedMLP(FeedForward):
         y = g * sigmoid(alpha * g) * (u + 1);  out = W_down y + b_down
     ``limit`` and ``alpha`` (default 1.702, which makes g * sigmoid(alpha g) close to gelu) are parameters; so are the
     tensor names (``names``: gate, up, down; each bias is the matrix's name + ``bias_suffix``). gate and up are
-    stacked and interleaved as in ``GatedMLP``. The activation is fp32 arithmetic on the product's stored result.
+    stacked and interleaved as in ``GatedMLP``, and as there the activation (biases and limits included) runs in the
+    epilogue of the first product for decode rows and for prompt portions in bfloat16; elsewhere a kernel of its own
+    applies it to the stored product. Either way it is fp32 arithmetic on the product rounded to the compute dtype.
     ``output_bias`` is the down projection's bias; a caller that adds it itself (an arrangement that normalises the
     result anyway) calls ``forward(..., add_bias=False)``."""
     capturable = True
@@ -187,10 +189,18 @@ class LimitedGatedMLP(FeedForward):
 
     def forward(self, x, ctx, add_bias=True):
         T = x.shape[0]
-        gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
-        linear(x, self.gate_up, gu, ctx.status)
         act = ctx.buf("ffn_act", (T, self.inter), self.dtype)
-        ops.glu_limited(gu, self.gate_up_bias, act, self.group, self.limit, self.alpha)
+        fused = self.group == INTERLEAVE and act.dtype == torch.bfloat16
+        if fused and linear_mod.USE_SKINNY and ops.gemm_skinny_ok(x, self.gate_up, act):
+            # decode rows: biases, limits and the gate in the epilogue of the weight-streaming product
+            ops.gemm_skinny_glu_limited(x, self.gate_up, self.gate_up_bias, act, self.limit, self.alpha, checked=True)
+        elif (fused and USE_TC05_GEMM and linear_mod.USE_OWN_GEMM and T >= linear_mod.OWN_GEMM_MIN_ROWS
+                and ops.gemm_tc05_available() and ops.gemm_tc05_ok(x, self.gate_up, act)):
+            ops.gemm_tc05_glu_limited(x, self.gate_up, self.gate_up_bias, act, self.limit, self.alpha, ctx.status)   # prompt portions
+        else:
+            gu = ctx.buf("ffn_gate_up", (T, 2 * self.inter), self.dtype)
+            linear(x, self.gate_up, gu, ctx.status)
+            ops.glu_limited(gu, self.gate_up_bias, act, self.group, self.limit, self.alpha)
         out = ctx.buf("delta", (T, self.hidden), self.dtype)
         linear(act, self.down, out, ctx.status)
         if add_bias:

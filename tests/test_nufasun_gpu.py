@@ -342,7 +342,8 @@ def test_delta_rule_kernels_in_portions(H, G, dk, dv, taps):
         g = h // (H // G)
         o = pn.delta_rule_head(q[:, g], k[:, g], v[:, h], beta[:, h], decay[:, h])
         want[:, h] = pn.rms_norm(o, norm_w.double(), 1e-5) * gate[:, h] * torch.sigmoid(gate[:, h])
-    conv_off = H * dk * dv
+    assert ops.delta_state_floats(dk, dv) == ops.delta_state_floats_of_library(dk, dv) >= dk * dv
+    conv_off = H * ops.delta_state_floats(dk, dv)
     state = torch.randn(3, conv_off + (taps - 1) * C, device=DEV)          # stale contents
     got = torch.zeros(T, H * dv, device=DEV)
     ud = u.to(DEV)
@@ -359,7 +360,7 @@ def test_delta_rule_kernels_in_portions(H, G, dk, dv, taps):
         q_start, ctx_len, slots = ints(0, no, R), ints(po + no, p + n), ints(2, 1)
         xc = torch.zeros(R, C, device=DEV)
         ops.causal_conv(rows[:, :C], conv_w.to(DEV), zero_b, state, conv_off, xc, positions, row_seq, q_start, ctx_len, slots, 2)
-        bg = torch.zeros(R, 2 * H, device=DEV)
+        bg = torch.zeros(R, 2 * H + G, device=DEV)
         ops.delta_prepare(xc, rows, C + H * dv, C + H * dv + H, a_log.to(DEV), dt_bias.to(DEV), bg, G, H, dk, dk ** -0.5)
         y = torch.zeros(R, H * dv, device=DEV)
         ops.delta_scan(xc, bg, state, y, q_start, ctx_len, slots, 2, G, H, dk, dv)

@@ -75,7 +75,9 @@ def test_checkpoint_names_shapes_cache_and_state(tmp_path):
     # a pass of its own for each run of a looped layer; both maps' keys, one value head for the two
     assert needs[1] == needs[4] and needs[1].num_kv_heads == 4 and needs[1].v_heads == 2 and needs[1].window == 21
     assert needs[1].head_dim == 32 and needs[1].v_dim == 16 and needs[7].window is None
-    assert states[0].shape == (4 * 24 * 16 + 3 * (2 * 2 * 24 + 4 * 16),) and states[2] == states[5] and states[1] is None
+    from llm_steadyinfer_b200.csrc import ops
+    assert ops.delta_state_floats(24, 16) == 32 * 16 and ops.delta_state_floats(128, 128) == 128 * 128   # 24 rows: 8 parts of 4 rows; 128: 32 parts of 4
+    assert states[0].shape == (4 * 4 * 128 + 3 * (2 * 2 * 24 + 4 * 16),) and states[2] == states[5] and states[1] is None
     lam = model.blocks[1].mixer.lam
     cfg, w = pn.read_model_folder(folder)
     want = (torch.exp((w["l1.mix.lq1"] * w["l1.mix.lk1"]).sum()) - torch.exp((w["l1.mix.lq2"] * w["l1.mix.lk2"]).sum())).item() + 0.2
