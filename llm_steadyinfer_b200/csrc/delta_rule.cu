@@ -69,7 +69,7 @@ SI_EXPORT int si_delta_prepare(float* xc, long long xc_stride, const void* ba, i
   return si_last_error();
 }
 
-#define DELTA_CHUNK 16
+#define DELTA_CHUNK 32
 
 __device__ __forceinline__ void delta_cp4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
@@ -79,8 +79,9 @@ __device__ __forceinline__ void delta_cp16(float* dst, const float* src) {
 }
 
 // The shape for a state of dk x dv: rows a thread (RPT, a multiple of 4) and parts a column (NP, a power of two up to 32,
-// RPT * NP >= dk). Few rows a thread and many parts: a sequence's tokens are a chain of dependent steps, and what
-// shortens the chain and gives a multiprocessor more warps to choose from counts for more than the shuffles it adds.
+// RPT * NP >= dk): about sixteen parts. A sequence's tokens are a chain of dependent steps; few rows a thread shorten the
+// chain and give a multiprocessor warps to choose from, many parts cost shuffles (measured at 128 x 128, 16 heads, one
+// sequence of 2,048 tokens: 16 rows in 8 parts 1.54 ms, 4 rows in 32 parts 0.69 ms).
 // Thread (column j, part p) keeps, for c < RPT / 4, the four rows (c * NP + p) * 4 .. + 3 of column j (so that the parts
 // read neighbouring 16-byte words of q and k). A head's state lies in the slot as [RPT][dv][NP]: entry
 // ((r * dv + j) * NP + p) is the thread's r-th row, so that a block reads and writes whole lines whatever cut of the
@@ -88,7 +89,7 @@ __device__ __forceinline__ void delta_cp16(float* dst, const float* src) {
 struct DeltaShape { int rpt, np; };
 static DeltaShape delta_shape(int dk) {
   DeltaShape s;
-  s.rpt = ((dk + 31) / 32 + 3) / 4 * 4;
+  s.rpt = ((dk + 15) / 16 + 3) / 4 * 4;
   int parts = 1;
   while (parts * s.rpt < dk) parts *= 2;
   s.np = parts;
@@ -96,7 +97,7 @@ static DeltaShape delta_shape(int dk) {
 }
 // fp32 entries of one head's state in a slot
 SI_EXPORT long long si_delta_state_floats(int dk, int dv) {
-  if (dk <= 0 || dv <= 0 || dk > 1024) return -1;
+  if (dk <= 0 || dv <= 0 || dk > 512) return -1;
   const DeltaShape s = delta_shape(dk);
   return (long long)s.rpt * s.np * dv;
 }
@@ -133,36 +134,30 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(const float* __restrict
   __syncthreads();
   const size_t q_off = (size_t)g * dk, k_off = (size_t)(G + g) * dk, v_off = (size_t)2 * G * dk + (size_t)h * dv + j0;
   const bool wide = dk % 4 == 0 && xc_stride % 4 == 0 && ((uintptr_t)xc & 15) == 0;      // q and k rows in 16-byte pieces
-  // what this thread copies of every token, found once: its first piece of [q | k] (further ones lie blockDim pieces
-  // on), and one of the token's small values (a value column, or beta, g, q . k)
+  // a warp fetches whole tokens (every nwarps-th of the chunk): the copies' bookkeeping is then paid once a token by one
+  // warp, not by every warp
   const int unit = wide ? 4 : 1, pieces = 2 * dk / unit, per_half = dk / unit;
-  const int extra = threadIdx.x < cols + 3 ? threadIdx.x : -1;
-  long long extra_src = 0;
-  int extra_dst = 0;
-  bool extra_bg = false;
-  if (extra >= cols) {
-    const int w = extra - cols;
-    extra_bg = true;
-    extra_src = w == 0 ? h : w == 1 ? H + h : 2 * H + g;
-    extra_dst = per_tok - 4 + w;
-  } else if (extra >= 0) {
-    extra_src = (long long)v_off + extra;
-    extra_dst = 2 * dkp + extra;
-  }
-  const bool extra_ok = extra >= 0 && (extra_bg || j0 + extra < dv);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   auto fetch = [&](int c0, int buf) {
-    float* dst = sm + (size_t)buf * DELTA_CHUNK * per_tok;
     const int cn = min(DELTA_CHUNK, n - c0);
-    const float* row = xc + (size_t)(row0 + c0) * xc_stride;
-    const float* bgr = bg + (size_t)(row0 + c0) * bg_width;
-    for (int tt = 0; tt < cn; ++tt, row += xc_stride, bgr += bg_width, dst += per_tok) {
-      for (int t = threadIdx.x; t < pieces; t += blockDim.x) {
+    for (int tt = warp; tt < cn; tt += nwarps) {
+      float* dst = sm + ((size_t)buf * DELTA_CHUNK + tt) * per_tok;
+      const float* row = xc + (size_t)(row0 + c0 + tt) * xc_stride;
+      const float* bgr = bg + (size_t)(row0 + c0 + tt) * bg_width;
+      for (int t = lane; t < pieces; t += 32) {
         const bool is_q = t < per_half;
         const int i = (is_q ? t : t - per_half) * unit;
         if (wide) delta_cp16(dst + (is_q ? 0 : dkp) + i, row + (is_q ? q_off : k_off) + i);
         else delta_cp4(dst + (is_q ? 0 : dkp) + i, row + (is_q ? q_off : k_off) + i);
       }
-      if (extra_ok) delta_cp4(dst + extra_dst, (extra_bg ? bgr : row) + extra_src);
+      for (int e = lane; e < cols + 3; e += 32) {
+        if (e < cols) {
+          if (j0 + e < dv) delta_cp4(dst + 2 * dkp + e, row + v_off + e);
+        } else {                                     // beta, g, q . k of this head
+          const int w = e - cols;
+          delta_cp4(dst + per_tok - 4 + w, bgr + (w == 0 ? h : w == 1 ? H + h : 2 * H + g));
+        }
+      }
     }
     asm volatile("cp.async.commit_group;\n" ::);
   };
@@ -175,6 +170,7 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(const float* __restrict
     if (c0 + DELTA_CHUNK < n) fetch(c0 + DELTA_CHUNK, buf ^ 1);
     const float* tok = sm + (size_t)buf * DELTA_CHUNK * per_tok;
     float* yp = y + (size_t)(row0 + c0) * y_stride + (size_t)h * dv + j;
+#pragma unroll 2
     for (int tt = 0; tt < cn; ++tt, tok += per_tok, yp += y_stride) {
       const float4* q4 = reinterpret_cast<const float4*>(tok) + p;
       const float4* k4 = reinterpret_cast<const float4*>(tok + dkp) + p;
@@ -220,7 +216,7 @@ SI_EXPORT int si_delta_scan(const float* xc, long long xc_stride, const float* b
                             long long state_stride, float* y, long long y_stride, const int* q_start, const int* ctx_len,
                             const int* slots, int num_seqs, int G, int H, int dk, int dv, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
-  if (G <= 0 || H % G || dk <= 0 || dv <= 0 || dk > 1024 || H > 65535 || bg_width < 2 * H + G) return -2;
+  if (G <= 0 || H % G || dk <= 0 || dv <= 0 || dk > 512 || H > 65535 || bg_width < 2 * H + G) return -2;
   const DeltaShape sh = delta_shape(dk);
   if (sh.rpt * sh.np < dk) return -2;
   if (state_stride < (long long)H * sh.rpt * sh.np * dv) return -2;
@@ -249,7 +245,7 @@ SI_EXPORT int si_delta_scan(const float* xc, long long xc_stride, const float* b
     si_launch(delta_scan_kernel<R>, grid, block, smem, stream, xc, xc_stride, bg, bg_width, state, state_stride, y,  \
               y_stride, q_start, ctx_len, slots, G, H, dk, dv, np, cols);                                            \
   }
-  switch (sh.rpt) {                          // dk up to 2048: up to 64 rows a thread
+  switch (sh.rpt) {                          // dk up to 512: up to 32 rows a thread
     case 4: DELTA_LAUNCH(4) break;
     case 8: DELTA_LAUNCH(8) break;
     case 12: DELTA_LAUNCH(12) break;

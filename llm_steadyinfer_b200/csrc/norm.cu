@@ -284,10 +284,122 @@ __global__ void __launch_bounds__(256) add_norm_general_kernel(float* __restrict
     o[i] = from_f32<TX>(to_f32<TW>(weight[i]) * (row_cache[i] * inv));
 }
 
+// The same with the row in registers: widths that are multiples of 8 with 16-byte aligned tensors; every thread moves
+// 8 elements at a time with 16-byte loads, all of a row's loads in flight before the first use.
+template <typename TX, typename TW, int CHUNKS>
+__global__ void __launch_bounds__(512) add_norm_general_vec_kernel(float* __restrict__ resid, const TX* __restrict__ delta,
+    const float* __restrict__ delta_bias, const TW* __restrict__ delta_weight, float delta_eps,
+    const float* __restrict__ extra, const float* __restrict__ vec, const int* __restrict__ rows,
+    const TW* __restrict__ weight, TX* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_prologue();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* h = resid + (size_t)src * hidden;
+  const int nchunks = hidden >> 3;
+  Vec8<float> x[CHUNKS], d[CHUNKS];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      x[c].load(h + ch * 8);
+      if (delta) {
+        Vec8<TX> t;
+        t.load(delta + (size_t)src * hidden + ch * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d[c].v[i] = t.v[i];
+        if (delta_bias) {
+          Vec8<float> b;
+          b.load(delta_bias + ch * 8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d[c].v[i] += b.v[i];
+        }
+      }
+    }
+  }
+  if (delta && delta_weight) {
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+      if (threadIdx.x + c * blockDim.x < nchunks)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += d[c].v[i] * d[c].v[i];
+    ss = block_sum(ss, scratch);
+    const float dscale = rsqrtf(ss / (float)hidden + delta_eps);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunks) {
+        Vec8<TW> w;
+        w.load(delta_weight + ch * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d[c].v[i] = w.v[i] * (d[c].v[i] * dscale);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      if (delta)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[c].v[i] += d[c].v[i];
+      if (extra) {
+        Vec8<float> e;
+        e.load(extra + (size_t)src * hidden + ch * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[c].v[i] += e.v[i];
+      }
+      if (vec) {
+        Vec8<float> e;
+        e.load(vec + ch * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[c].v[i] += e.v[i];
+      }
+      if (!rows) x[c].store(h + ch * 8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[c].v[i] * x[c].v[i];
+    }
+  }
+  if (!out) return;
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TX* o = out + (size_t)r * hidden;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      Vec8<TW> w;
+      w.load(weight + ch * 8);
+      Vec8<TX> yv;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) yv.v[i] = w.v[i] * (x[c].v[i] * inv);
+      yv.store(o + ch * 8);
+    }
+  }
+}
+
 template <typename TX, typename TW>
 static int general_launch(float* resid, const void* delta, const float* delta_bias, const void* delta_weight, float delta_eps,
                           const float* extra, const float* vec, const int* rows, const void* weight, void* out, int num_rows,
                           int hidden, float eps, cudaStream_t stream) {
+  const auto al = [](const void* p) { return ((uintptr_t)p % 16) == 0; };
+  if (hidden % 8 == 0 && hidden <= 4 * 8 * 512 && al(resid) && al(delta) && al(delta_bias) && al(delta_weight) && al(extra) &&
+      al(vec) && al(weight) && al(out)) {
+    const int nchunks = hidden / 8;
+    int threads = nchunks > 256 ? 512 : (nchunks > 128 ? 256 : 128);
+    if (num_rows >= 1024 && nchunks <= 1024) threads = min(threads, 256);   // many rows: more blocks per SM
+    const int per = (nchunks + threads - 1) / threads;
+#define SI_GENERAL_VEC(C)                                                                                             \
+    si_launch(add_norm_general_vec_kernel<TX, TW, C>, dim3(num_rows), dim3(threads), 0, stream, resid, (const TX*)delta,   \
+              delta_bias, (const TW*)delta_weight, delta_eps, extra, vec, rows, (const TW*)weight, (TX*)out, hidden, eps)
+    if (per <= 1) SI_GENERAL_VEC(1);
+    else if (per <= 2) SI_GENERAL_VEC(2);
+    else SI_GENERAL_VEC(4);
+#undef SI_GENERAL_VEC
+    return si_last_error();
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return -2;
   static size_t configured = 0;

@@ -1288,9 +1288,9 @@ def delta_state_floats(dk: int, dv: int) -> int:
     the rows padded to rows a thread x parts). The same rule as ``delta_shape`` in delta_rule.cu, restated here so that a
     model's state size is known without the library; ``delta_state_floats_of_library`` asks the library, and a test holds
     the two together."""
-    if dk <= 0 or dv <= 0 or dk > 1024:
+    if dk <= 0 or dv <= 0 or dk > 512:
         raise KernelError(f"delta_scan: a state of {dk} x {dv} is outside what the kernel supports")
-    r = (-(-dk // 32) + 3) // 4 * 4
+    r = (-(-dk // 16) + 3) // 4 * 4
     parts = 1
     while parts * r < dk:
         parts *= 2

@@ -15,50 +15,53 @@
 #include "common.cuh"
 #include <math.h>
 
-template <typename T>
+// A lane takes pairs of entries: the two of a rotation where the vector is rotated, neighbours elsewhere. Every entry is
+// read once, kept in registers over the warp's sum, and written once, so source and destination may be the same.
+// ITEMS: pairs a lane (1, 2, 4 or 10: sizes up to 64, 128, 256, 640)
+template <typename T, int ITEMS>
 __device__ __forceinline__ void norm_rotate_vector(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ w,
                                                    float eps, const float* __restrict__ sc_table, int rd, int interleaved,
                                                    int dk, int lane) {
-  float inv = 1.f;
-  if (w) {
-    float ss = 0.f;
-    for (int i = lane; i < dk; i += 32) {
-      const float x = to_f32<T>(src[i]);
-      ss += x * x;
-    }
-    inv = rsqrtf(warp_sum(ss) / (float)dk + eps);
-  }
   const int half = rd / 2;
-  // every entry is read (with its partner) before any entry of the vector is written: in place is safe only
-  // because a lane's results are kept until the warp has read everything
-  float keep[20];
+  const int items = interleaved ? (dk + 1) / 2 : half + (dk - rd + 1) / 2;
+  float xa[ITEMS], xb[ITEMS];
+  float ss = 0.f;
 #pragma unroll
-  for (int c = 0; c < 20; ++c) {
-    const int i = lane + 32 * c;
-    if (i >= dk) break;
-    float y = to_f32<T>(src[i]) * inv * (w ? w[i] : 1.f);
-    if (i < rd) {
-      int f, partner;
-      bool first;
-      if (interleaved) { f = i >> 1; first = (i & 1) == 0; partner = i ^ 1; }
-      else { first = i < half; f = first ? i : i - half; partner = first ? i + half : i - half; }
-      const float z = to_f32<T>(src[partner]) * inv * (w ? w[partner] : 1.f);
-      const float s = sc_table[f], c2 = sc_table[half + f];
-      y = first ? y * c2 - z * s : y * c2 + z * s;
-    }
-    keep[c] = y;
+  for (int c = 0; c < ITEMS; ++c) {
+    const int t = lane + 32 * c;
+    int ia, ib;
+    if (interleaved) { ia = 2 * t; ib = ia + 1; }
+    else if (t < half) { ia = t; ib = t + half; }
+    else { ia = rd + 2 * (t - half); ib = ia + 1; }
+    xa[c] = (t < items) ? to_f32<T>(src[ia]) : 0.f;
+    xb[c] = (t < items && ib < dk) ? to_f32<T>(src[ib]) : 0.f;
+    ss = fmaf(xa[c], xa[c], fmaf(xb[c], xb[c], ss));
   }
-  __syncwarp();
+  const float inv = w ? rsqrtf(warp_sum(ss) / (float)dk + eps) : 1.f;
 #pragma unroll
-  for (int c = 0; c < 20; ++c) {
-    const int i = lane + 32 * c;
-    if (i >= dk) break;
-    dst[i] = from_f32<T>(keep[c]);
+  for (int c = 0; c < ITEMS; ++c) {
+    const int t = lane + 32 * c;
+    if (t >= items) continue;
+    int ia, ib, f;
+    bool rot;
+    if (interleaved) { ia = 2 * t; ib = ia + 1; f = t; rot = ia < rd; }
+    else if (t < half) { ia = t; ib = t + half; f = t; rot = true; }
+    else { ia = rd + 2 * (t - half); ib = ia + 1; f = 0; rot = false; }
+    const bool has_b = ib < dk;
+    float ya = xa[c] * inv * (w ? w[ia] : 1.f);
+    float yb = has_b ? xb[c] * inv * (w ? w[ib] : 1.f) : 0.f;
+    if (rot) {
+      const float sn = sc_table[f], cs = sc_table[half + f];
+      const float ra = ya * cs - yb * sn, rb = yb * cs + ya * sn;
+      ya = ra; yb = rb;
+    }
+    dst[ia] = from_f32<T>(ya);
+    if (has_b) dst[ib] = from_f32<T>(yb);
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(128) qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const float* __restrict__ q_w,
+template <typename T, int ITEMS>
+__global__ void __launch_bounds__(256) qk_prepare_kernel(T* __restrict__ rows, long long row_stride, const float* __restrict__ q_w,
     const float* __restrict__ k_w, float eps, const float* __restrict__ inv_freq, int rd, int interleaved,
     const int* __restrict__ positions, const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_width,
     T* __restrict__ k_cache, T* __restrict__ v_cache, int num_pages, int page_size, int num_seqs, int NQ, int NK, int NV,
@@ -94,11 +97,11 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(T* __restrict__ rows, l
     if (vec < NQ) {
       const int head = vec / maps, m = vec - head * maps;
       const int place = ((head / ratio) * maps + m) * ratio + head % ratio;       // maps == 1: vec itself
-      norm_rotate_vector<T>(src, q_out + (size_t)t * q_out_stride + (size_t)place * dk, q_w, eps, sc_table, rd, interleaved,
+      norm_rotate_vector<T, ITEMS>(src, q_out + (size_t)t * q_out_stride + (size_t)place * dk, q_w, eps, sc_table, rd, interleaved,
                             dk, lane);
     } else if (page >= 0) {
       T* dst = k_cache + (((size_t)page * NK + (vec - NQ)) * page_size + off) * dk;
-      norm_rotate_vector<T>(src, dst, k_w, eps, sc_table, rd, interleaved, dk, lane);
+      norm_rotate_vector<T, ITEMS>(src, dst, k_w, eps, sc_table, rd, interleaved, dk, lane);
     }
   }
   if (page >= 0 && v_cache) {
@@ -119,15 +122,24 @@ SI_EXPORT int si_qk_prepare(void* rows, int dtype, long long row_stride, const f
   if (dk <= 0 || dk > 640 || rd < 0 || rd > dk || rd % 2 || (rd > 0 && !inv_freq)) return -2;
   if (maps < 1 || NK <= 0 || NQ % NK || NK % maps || (maps > 1 && q_out == rows)) return -2;
   const size_t smem = (size_t)(rd > 0 ? rd : 1) * sizeof(float);
-  if (dtype == SI_BF16)
-    si_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), smem, stream, (__nv_bfloat16*)rows, row_stride, q_w,
-              k_w, eps, inv_freq, rd, interleaved, positions, row_seq, block_table, table_width, (__nv_bfloat16*)k_cache,
-              (__nv_bfloat16*)v_cache, num_pages, page_size, num_seqs, NQ, NK, NV, dk, dv, (__nv_bfloat16*)q_out, q_out_stride,
-              maps, status);
-  else
-    si_launch(qk_prepare_kernel<float>, dim3(num_tokens), dim3(128), smem, stream, (float*)rows, row_stride, q_w, k_w, eps,
-              inv_freq, rd, interleaved, positions, row_seq, block_table, table_width, (float*)k_cache, (float*)v_cache,
-              num_pages, page_size, num_seqs, NQ, NK, NV, dk, dv, (float*)q_out, q_out_stride, maps, status);
+  // a warp a vector at a time; eight warps where there are vectors for them, so that a row's loads are in flight together
+  const dim3 grid(num_tokens), block(NQ + NK >= 8 ? 256 : 128);
+#define QK_LAUNCH(T, ITEMS)                                                                                              \
+  si_launch(qk_prepare_kernel<T, ITEMS>, grid, block, smem, stream, (T*)rows, row_stride, q_w, k_w, eps, inv_freq, rd,      \
+            interleaved, positions, row_seq, block_table, table_width, (T*)k_cache, (T*)v_cache, num_pages, page_size,   \
+            num_seqs, NQ, NK, NV, dk, dv, (T*)q_out, q_out_stride, maps, status)
+  if (dtype == SI_BF16) {
+    if (dk <= 64) QK_LAUNCH(__nv_bfloat16, 1);
+    else if (dk <= 128) QK_LAUNCH(__nv_bfloat16, 2);
+    else if (dk <= 256) QK_LAUNCH(__nv_bfloat16, 4);
+    else QK_LAUNCH(__nv_bfloat16, 10);
+  } else {
+    if (dk <= 64) QK_LAUNCH(float, 1);
+    else if (dk <= 128) QK_LAUNCH(float, 2);
+    else if (dk <= 256) QK_LAUNCH(float, 4);
+    else QK_LAUNCH(float, 10);
+  }
+#undef QK_LAUNCH
   return si_last_error();
 }
 

@@ -43,8 +43,8 @@ class GatedDeltaRule(Mixer):
             raise ValueError(f"gated_delta: {self.H} heads are not a multiple of {self.G} query/key heads")
         if not 1 <= self.taps <= 17:
             raise ValueError(f"gated_delta: {self.taps} convolution taps are not supported (1 to 17)")
-        if self.dk > 1024:
-            raise ValueError("gated_delta: key sizes above 1024 are not supported")
+        if self.dk > 512:
+            raise ValueError("gated_delta: key sizes above 512 are not supported")
         self.nqk, self.nv = self.G * self.dk, self.H * self.dv
         self.channels = 2 * self.nqk + self.nv                     # what the convolution runs over: [q | k | v]
         self.g_off = self.channels

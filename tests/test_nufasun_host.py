@@ -76,7 +76,7 @@ def test_checkpoint_names_shapes_cache_and_state(tmp_path):
     assert needs[1] == needs[4] and needs[1].num_kv_heads == 4 and needs[1].v_heads == 2 and needs[1].window == 21
     assert needs[1].head_dim == 32 and needs[1].v_dim == 16 and needs[7].window is None
     from llm_steadyinfer_b200.csrc import ops
-    assert ops.delta_state_floats(24, 16) == 32 * 16 and ops.delta_state_floats(128, 128) == 128 * 128   # 24 rows: 8 parts of 4 rows; 128: 32 parts of 4
+    assert ops.delta_state_floats(24, 16) == 32 * 16 and ops.delta_state_floats(128, 128) == 128 * 128   # 24 rows: 8 parts of 4 rows; 128: 16 parts of 8
     assert states[0].shape == (4 * 4 * 128 + 3 * (2 * 2 * 24 + 4 * 16),) and states[2] == states[5] and states[1] is None
     lam = model.blocks[1].mixer.lam
     cfg, w = pn.read_model_folder(folder)
