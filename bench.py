@@ -253,8 +253,8 @@ def _llama_twin():
 
 
 # ---- the Nufasun design beside the closest existing models ---------------------------------------------------
-_DIFF = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 50.0, "diff": 0.3,
-         "mask": {"size": 4096}, "rot": {"base": 500000.0, "dims": 64}}
+_DIFF = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 30.0, "diff": 0.2,
+         "mask": {"size": 4096}, "rot": {"base": 10000.0, "dims": 64}}
 _DELTA = {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4}
 
 

@@ -55,7 +55,7 @@ MIXED_A = _model(331, 96, 1e-5, [
 MIXED_B = _model(500, 256, 2e-6, [
     _layer("attention", _attn(8, 2, 64, 32, 70, 32, base=250.0), ff=384),
     _layer("delta", _delta(8, 2, 32, 64, 4), ff=384, limit=2.0),
-    _layer("attention", _attn(4, 1, 48, 80, 33, 48, softcap=50.0, diff=0.1), ff=128),
+    _layer("attention", _attn(4, 1, 48, 80, 33, 48, softcap=40.0, diff=0.1), ff=128),
     _layer("delta", _delta(4, 4, 64, 32, 3), ff=None),
 ], loop=(0, 2, 3), scale=8.0, cap=20.0)
 # sizes that are multiples of nothing useful, no loop, no cap

@@ -374,7 +374,7 @@ def test_delta_rule_kernels_in_portions(H, G, dk, dv, taps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("width", [70, 192, 2048])
+@pytest.mark.parametrize("width", [70, 200, 2048])
 def test_the_add_in_its_general_form(width, dtype):
     """A normalised delta with a bias, the embedding's output and a vector join the stream; the stream's own norm behind
     it; and the same for chosen rows only, which leaves the stream as it is."""
