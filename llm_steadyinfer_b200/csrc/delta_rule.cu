@@ -105,11 +105,11 @@ SI_EXPORT long long si_delta_state_floats(int dk, int dv) {
 // RPT: rows of a column that a thread keeps, as RPT / 2 pairs (the sums and the update run two rows at a time on the
 // packed fp32 instructions). Shared memory: two buffers of CHUNK tokens of [q: RPT * NP | k: RPT * NP | v: cols |
 // beta, g, q . k, -] (rows beyond dk stay zero), filled by cp.async one chunk ahead of the sums.
-template <int RPT>
+template <int RPT, int NP>
 __global__ void __launch_bounds__(256) delta_scan_kernel(const float* __restrict__ xc, long long xc_stride,
     const float* __restrict__ bg, int bg_width, float* __restrict__ state, long long state_stride, float* __restrict__ y,
     long long y_stride, const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ slots,
-    int G, int H, int dk, int dv, int NP, int cols) {
+    int G, int H, int dk, int dv, int cols) {
   extern __shared__ __align__(16) float sm[];
   pdl_prologue();
   const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
@@ -188,11 +188,9 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(const float* __restrict
       }
       float sk = sk0.x + sk0.y, sq = sq0.x + sq0.y;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        if (o < NP) {                           // the same for every thread
-          sk += __shfl_xor_sync(0xffffffffu, sk, o);
-          sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        }
+      for (int o = 1; o < NP; o <<= 1) {
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
       }
       const float4 sc = *reinterpret_cast<const float4*>(tok + per_tok - 4);      // beta, g, q . k
       const float vj = col_ok ? tok[2 * dkp + jl] : 0.f;
@@ -233,28 +231,41 @@ SI_EXPORT int si_delta_scan(const float* xc, long long xc_stride, const float* b
   const size_t smem = (size_t)2 * DELTA_CHUNK * (2 * sh.np * sh.rpt + ((cols + 3) & ~3) + 4) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   const dim3 grid(num_seqs, H, zb), block(threads);
-  const int np = sh.np;
-#define DELTA_LAUNCH(R)                                                                                              \
+#define DELTA_LAUNCH(R, P)                                                                                           \
   {                                                                                                                  \
     static size_t configured = 0;                                                                                    \
     if (smem > 48 * 1024 && smem > configured) {                                                                     \
-      if (cudaFuncSetAttribute(delta_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      if (cudaFuncSetAttribute(delta_scan_kernel<R, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return -2;                                                                                                   \
       configured = smem;                                                                                             \
     }                                                                                                                \
-    si_launch(delta_scan_kernel<R>, grid, block, smem, stream, xc, xc_stride, bg, bg_width, state, state_stride, y,  \
-              y_stride, q_start, ctx_len, slots, G, H, dk, dv, np, cols);                                            \
+    si_launch(delta_scan_kernel<R, P>, grid, block, smem, stream, xc, xc_stride, bg, bg_width, state, state_stride, y, \
+              y_stride, q_start, ctx_len, slots, G, H, dk, dv, cols);                                                \
   }
-  switch (sh.rpt) {                          // dk up to 512: up to 32 rows a thread
-    case 4: DELTA_LAUNCH(4) break;
-    case 8: DELTA_LAUNCH(8) break;
-    case 12: DELTA_LAUNCH(12) break;
-    case 16: DELTA_LAUNCH(16) break;
-    case 20: DELTA_LAUNCH(20) break;
-    case 24: DELTA_LAUNCH(24) break;
-    case 28: DELTA_LAUNCH(28) break;
-    case 32: DELTA_LAUNCH(32) break;
-    default: return -2;
+  // (rows a thread, parts a column) as delta_shape gives them: four rows in 1 to 16 parts up to dk = 64, then 16 parts
+  if (sh.np < 16) {
+    if (sh.rpt != 4) return -2;
+    switch (sh.np) {
+      case 1: DELTA_LAUNCH(4, 1) break;
+      case 2: DELTA_LAUNCH(4, 2) break;
+      case 4: DELTA_LAUNCH(4, 4) break;
+      case 8: DELTA_LAUNCH(4, 8) break;
+      default: return -2;
+    }
+  } else if (sh.np == 16) {
+    switch (sh.rpt) {                        // dk up to 512: up to 32 rows a thread
+      case 4: DELTA_LAUNCH(4, 16) break;
+      case 8: DELTA_LAUNCH(8, 16) break;
+      case 12: DELTA_LAUNCH(12, 16) break;
+      case 16: DELTA_LAUNCH(16, 16) break;
+      case 20: DELTA_LAUNCH(20, 16) break;
+      case 24: DELTA_LAUNCH(24, 16) break;
+      case 28: DELTA_LAUNCH(28, 16) break;
+      case 32: DELTA_LAUNCH(32, 16) break;
+      default: return -2;
+    }
+  } else {
+    return -2;
   }
 #undef DELTA_LAUNCH
   return si_last_error();
